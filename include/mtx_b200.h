@@ -351,6 +351,86 @@ int mtx_qkv_rope_append(const void* n, const void* wqkv, const int32_t* pos, con
  * at every call; see csrc/mtx_jax_ffi.cc).  A no-op when nothing moved. */
 int mtx_engine_rebind_state(mtx_engine* e, const mtx_decode_state* s);
 
+/* ---- layered models: a list of layer descriptors, ragged batches, a paged cache --------------------------------------------
+ *
+ * For decoders whose layers are not copies of one block (sizes, windows and sublayers that differ from layer to layer), served
+ * from the page pools of the page manager.  One step takes ANY mix of rows: a portion of a prompt is a run of rows with
+ * consecutive positions of one page group, a decoded token a single row; rows of different groups sit side by side.  The
+ * residual stream, the norms and the attention weights are fp32; `float32` = 1 makes the matrix products, the activations and
+ * the cache fp32 too (weights are then fp32 arrays), 0 keeps them bfloat16 with fp32 accumulation. */
+
+#define MTX_MIXER_WINDOW_SIGMOID 1 /* csrc/window_attention.cuh */
+
+typedef struct {
+  int32_t mixer;        /* MTX_MIXER_* */
+  int32_t heads;        /* H query heads */
+  int32_t kv_heads;     /* G key / value heads; query head h reads head h / (H / G) */
+  int32_t dim;          /* per-head size of queries and keys */
+  int32_t vdim;         /* per-head size of values */
+  int32_t window;       /* a query at position i sees the keys j with 0 <= i - j < window */
+  int32_t value_mix;    /* 0 none; 1 this layer's values are kept for later layers; 2 v = (1 - lambda) v + lambda kept */
+  int32_t ff;           /* hidden size of the gated feed-forward; 0 = the layer has none */
+  float scale;          /* multiplies <q, k> */
+  float softcap;        /* cap * tanh(score / cap); 0 = off */
+  float value_lambda;
+  float gain1, gain2;   /* the single gains of the norms on the mixer's / the feed-forward's output */
+  const void* wqkv;     /* [H*dim + G*dim + G*vdim, width] */
+  const float* bqkv;    /* [H*dim + G*dim + G*vdim] or NULL */
+  const float* q_norm;  /* [dim] or NULL */
+  const float* k_norm;  /* [dim] or NULL */
+  const float* dist_bias; /* [window, H]: added to the score of the key at distance i - j */
+  const float* head_bias; /* [H] or NULL */
+  const float* talk;    /* [H, H] mixing of the heads' weights, or NULL */
+  const void* wo;       /* [width, H*vdim] */
+  const void* w_gate_up; /* [2*ff, width], rows interleaved: 2f = gate f, 2f + 1 = up f */
+  const void* w_down;   /* [width, ff] */
+  void* k_pages;        /* [G, num_pages, tokens_per_page, dim] */
+  void* v_pages;        /* [G, num_pages, tokens_per_page, vdim] */
+} mtx_layer_desc;
+
+typedef struct {
+  int32_t num_layers;
+  int32_t width;
+  int32_t vocab;
+  int32_t float32;             /* 1: true fp32 everywhere */
+  int32_t max_rows;            /* most rows of one step */
+  int32_t max_want;            /* most rows of one step whose logits are asked for */
+  int32_t num_groups;          /* page groups (decode slots) */
+  int32_t num_pages;
+  int32_t tokens_per_page;
+  int32_t max_pages_per_group;
+  float eps;
+  float embed_scale;
+  float final_gain;
+  const void* embedding;       /* [vocab, width] */
+  const void* head;            /* [vocab, width] */
+} mtx_layered_config;
+
+typedef struct {
+  int32_t rows;
+  const int32_t* token;        /* [rows] */
+  const int32_t* group;        /* [rows] page group of the row's sequence */
+  const int32_t* pos;          /* [rows] position in its sequence (from 0) */
+  const int32_t* page_map;     /* [num_groups, max_pages_per_group] (PageState.page_map) */
+  int32_t n_want;
+  const int32_t* want_rows;    /* [n_want] rows whose logits are written */
+  float* logits;               /* [n_want, vocab] */
+} mtx_ragged_batch;
+
+typedef struct mtx_layered mtx_layered; /* opaque */
+
+int mtx_layered_create(const mtx_layered_config* cfg, const mtx_layer_desc* layers, mtx_layered** out);
+int mtx_layered_destroy(mtx_layered* e);
+size_t mtx_layered_workspace_bytes(const mtx_layered* e);
+int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes);
+/* All layers for the rows of `b` (appending their keys / values to the pages), then the logits of the wanted rows. */
+int mtx_layered_step(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream stream);
+
+/* inference_utils.sampling (:66-111) on a logits matrix, without an engine: greedy / weighted / nucleus / top-k as
+ * mtx_sample_logits does it.  rng_state: 4 x uint32 device words ([0] = draw counter, [1..2] = seed); scratch: 5 * rows floats. */
+int mtx_sample_rows(const float* logits, int rows, long long ld, int vocab, int strategy, int top_k, float nucleus_p, float temperature,
+                    uint32_t* rng_state, int row_offset, void* scratch, int32_t* token_out, float* log_prob_out, mtx_stream stream);
+
 /* ---- misc ---------------------------------------------------------------------------------- */
 
 /* Measurement aid: grid-barrier timeline of the persistent step kernel.  While a device buffer of

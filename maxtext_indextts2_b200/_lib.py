@@ -108,6 +108,38 @@ class DecodeState(ctypes.Structure):
   ]
 
 
+MIXER_WINDOW_SIGMOID = 1
+
+
+class LayerDesc(ctypes.Structure):
+  """mtx_layer_desc (include/mtx_b200.h)."""
+
+  _fields_ = (
+      [(n, ctypes.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "window", "value_mix", "ff")]
+      + [(n, ctypes.c_float) for n in ("scale", "softcap", "value_lambda", "gain1", "gain2")]
+      + [(n, ctypes.c_void_p) for n in ("wqkv", "bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk", "wo", "w_gate_up", "w_down",
+                                        "k_pages", "v_pages")]
+  )
+
+
+class LayeredConfig(ctypes.Structure):
+  """mtx_layered_config."""
+
+  _fields_ = (
+      [(n, ctypes.c_int32) for n in ("num_layers", "width", "vocab", "float32", "max_rows", "max_want", "num_groups", "num_pages",
+                                     "tokens_per_page", "max_pages_per_group")]
+      + [(n, ctypes.c_float) for n in ("eps", "embed_scale", "final_gain")]
+      + [(n, ctypes.c_void_p) for n in ("embedding", "head")]
+  )
+
+
+class RaggedBatch(ctypes.Structure):
+  """mtx_ragged_batch."""
+
+  _fields_ = [("rows", ctypes.c_int32), ("token", ctypes.c_void_p), ("group", ctypes.c_void_p), ("pos", ctypes.c_void_p),
+              ("page_map", ctypes.c_void_p), ("n_want", ctypes.c_int32), ("want_rows", ctypes.c_void_p), ("logits", ctypes.c_void_p)]
+
+
 def sources() -> list[str]:
   return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh", ".cc"))) + [HEADER]
 
@@ -126,26 +158,64 @@ def _jaxlib_include() -> list[str]:
     return []
 
 
-def needs_build() -> bool:
-  if not os.path.isfile(LIB_PATH):
+UNITS = ("engine.cu", "layered.cu", "mtx_jax_ffi.cc")  # translation units of the library, compiled separately and linked
+
+
+def _unit_deps(path: str, seen=None) -> set:
+  """`path` and every file it includes with quotes, recursively."""
+  import re
+
+  seen = set() if seen is None else seen
+  path = os.path.normpath(path)
+  if path in seen or not os.path.isfile(path):
+    return seen
+  seen.add(path)
+  with open(path, "r", encoding="utf-8") as f:
+    for inc in re.findall(r'^\s*#\s*include\s+"([^"]+)"', f.read(), flags=re.M):
+      _unit_deps(os.path.join(os.path.dirname(path), inc), seen)
+  return seen
+
+
+def _object_path(unit: str) -> str:
+  return os.path.join(CSRC, "_build", os.path.splitext(unit)[0] + ".o")
+
+
+def _stale(target: str, deps) -> bool:
+  if not os.path.isfile(target):
     return True
-  built = os.path.getmtime(LIB_PATH)
-  return any(os.path.getmtime(s) > built for s in sources())
+  built = os.path.getmtime(target)
+  return any(os.path.getmtime(d) > built for d in deps)
+
+
+def needs_build() -> bool:
+  return _stale(LIB_PATH, sources())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-  """Compile every CUDA source of the package into ``libmtx_b200.so`` (sm_100a only)."""
+  """Compile every CUDA source of the package into ``libmtx_b200.so`` (sm_100a only): one object per translation unit
+  (rebuilt when it or a header it includes changed), compiled in parallel, then linked."""
   if not force and not needs_build():
     return LIB_PATH
   nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
   defines = ["-D" + d for d in os.environ.get("MTX_NVCC_DEFINES", "").split() if d]  # e.g. MTX_PK_EVENTS for tools/mega_trace.py
-  cmd = ([nvcc] + NVCC_FLAGS + defines + _jaxlib_include() + (["-Xptxas", "-v"] if verbose else []) +
-         ["-o", LIB_PATH, os.path.join(CSRC, "engine.cu"), os.path.join(CSRC, "mtx_jax_ffi.cc")])
+  os.makedirs(os.path.join(CSRC, "_build"), exist_ok=True)
+  flags = [f for f in NVCC_FLAGS if f != "--shared"] + defines + _jaxlib_include() + (["-Xptxas", "-v"] if verbose else [])
+  procs = []
+  for unit in UNITS:
+    src, obj = os.path.join(CSRC, unit), _object_path(unit)
+    if force or defines or _stale(obj, _unit_deps(src)):
+      cmd = [nvcc] + flags + ["-c", "-o", obj, src]
+      procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+  for cmd, proc in procs:
+    out, _ = proc.communicate()
+    if proc.returncode != 0:
+      raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + out)
+    if verbose:
+      print(out)
+  cmd = [nvcc, "--shared", "-o", LIB_PATH] + [_object_path(u) for u in UNITS]
   proc = subprocess.run(cmd, capture_output=True, text=True)
   if proc.returncode != 0:
-    raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
-  if verbose:
-    print(proc.stderr)
+    raise RuntimeError("link failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
   return LIB_PATH
 
 
@@ -235,6 +305,18 @@ def _declare(lib) -> None:
   lib.mtx_paged_insert.argtypes = [vp] * 5 + [i32] * 7 + [vp]
   lib.mtx_jax_ffi_available.restype = i32
   lib.mtx_jax_ffi_available.argtypes = []
+  lib.mtx_layered_create.restype = i32
+  lib.mtx_layered_create.argtypes = [c.POINTER(LayeredConfig), c.POINTER(LayerDesc), c.POINTER(vp)]
+  lib.mtx_layered_destroy.restype = i32
+  lib.mtx_layered_destroy.argtypes = [vp]
+  lib.mtx_layered_workspace_bytes.restype = sz
+  lib.mtx_layered_workspace_bytes.argtypes = [vp]
+  lib.mtx_layered_bind.restype = i32
+  lib.mtx_layered_bind.argtypes = [vp, vp, sz]
+  lib.mtx_layered_step.restype = i32
+  lib.mtx_layered_step.argtypes = [vp, c.POINTER(RaggedBatch), vp]
+  lib.mtx_sample_rows.restype = i32
+  lib.mtx_sample_rows.argtypes = [vp, i32, c.c_longlong, i32, i32, i32, f32, f32, vp, i32, vp, vp, vp, vp]
   lib.mtx_engine_rebind_state.restype = i32
   lib.mtx_engine_rebind_state.argtypes = [vp, c.POINTER(DecodeState)]
 

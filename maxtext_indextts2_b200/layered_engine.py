@@ -1,0 +1,397 @@
+"""MaxEngine for the layered designs (``pyconfig.LAYERED_BLOCKS``): the same engine API over ``mtx_layered_*``.
+
+A layered model is a list of layer descriptors (sizes, windows, sublayers that differ per layer), and its step takes a ragged
+batch: portions of prompts beside single decoded tokens, every row tagged with its page group and position.  So the three
+phases of the reference's engine are one device function here:
+
+* ``prefill``  -- the prompt's rows of ONE page group, written straight into that group's pages (no staging plane, no copy
+  at ``insert``); with ``existing_prefix`` the group simply grows (chunked prefill);
+* ``generate`` -- one row per decode slot (empty slots write the never-handed-out page 0);
+* ``step``     -- any mix of both, the entry point of continuous batching with chunked prompts and of ``trace_run``.
+
+The cache is the page manager's (``page_manager.PageManager``: pages handed out lowest index first, given back by
+``release_pages``); sampling is the framework's sampler on the step's logits (``mtx_sample_rows``).  Everything computed
+runs in ``libmtx_b200.so``; this file moves descriptors.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Any, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from . import page_manager
+from . import params as params_lib
+from .maxengine import ExistingPrefix, MaxEngine, ResultTokens  # noqa: F401  (same result types)
+
+_MIXERS = {"window_sigmoid": _lib.MIXER_WINDOW_SIGMOID}
+
+
+def design_module(config):
+  """The module that knows the design named by config.decoder_block."""
+  if config.decoder_block == "kifusun":
+    from . import kifusun
+
+    return kifusun
+  raise ValueError(f"decoder_block={config.decoder_block!r} is not a layered design")
+
+
+class LayeredParams:
+  """Device-resident weights of a layered model and the descriptor array handed to ``mtx_layered_create``."""
+
+  def __init__(self, plan: dict, config, device):
+    fp32 = config.dtype == "float32"
+    wt = torch.float32 if fp32 else torch.bfloat16
+    self.float32 = fp32
+    self.keep: List[torch.Tensor] = []
+
+    def mat(t):
+      t = t.to(device=device, dtype=wt).contiguous()
+      self.keep.append(t)
+      return t
+
+    def vec(t):
+      if t is None:
+        return None
+      t = t.to(device=device, dtype=torch.float32).contiguous()
+      self.keep.append(t)
+      return t
+
+    self.embedding, self.head = mat(plan["embedding"]), mat(plan["head"])
+    self.final_gain, self.embed_scale = float(plan["final_gain"]), float(plan["embed_scale"])
+    self.layers = []
+    for lp in plan["layers"]:
+      d = dict(lp)
+      for k in ("wqkv", "wo", "w_gate_up", "w_down"):
+        d[k] = mat(lp[k]) if lp[k] is not None else None
+      for k in ("bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk"):
+        d[k] = vec(lp.get(k))
+      self.layers.append(d)
+
+  def nbytes(self) -> int:
+    return sum(t.numel() * t.element_size() for t in self.keep)
+
+
+class LayeredEngine(MaxEngine):
+  """``MaxEngine(config)`` returns this class when ``config.decoder_block`` is a layered design."""
+
+  def __init__(self, config, devices: Any = None, use_cuda_graph: bool = True, vocab_shard: Optional[tuple] = None, gather: Any = None):
+    if vocab_shard is not None or int(config.vocab_parallelism) != 1:
+      raise ValueError("a layered model runs with vocab_parallelism=1")
+    self.config = config
+    self.device = _lib.require_cuda()
+    self.lib = _lib.load()
+    self.use_cuda_graph = use_cuda_graph
+    self._handle = ctypes.c_void_p()
+    self._params: Optional[LayeredParams] = None
+    self._state = None
+    self._paged, self._page_on_device, self._page_host_stale = True, False, False
+    self.page_manager = page_manager.PageManager(config)
+    self.page_state = self.page_manager.get_initial_page_state()
+    B = self.max_concurrent_decodes
+    self._max_rows = max(int(config.max_step_rows), B)
+    dev, i32 = self.device, torch.int32
+    self._tokens = torch.zeros(B, 1, dtype=i32, device=dev)
+    self._next_pos = torch.zeros(B, 1, dtype=i32, device=dev)
+    self._generated = torch.zeros(B, 1, dtype=i32, device=dev)
+    self._active = torch.zeros(B, 1, dtype=i32, device=dev)
+    self._result = torch.zeros(B, 3, dtype=i32, device=dev)
+    self._log_prob = torch.zeros(B, 1, dtype=torch.float32, device=dev) if config.return_log_prob else None
+    self._rng_state = torch.zeros(4, dtype=i32, device=dev)
+    self._slot_ids = torch.arange(B, dtype=i32, device=dev)
+    MP = self.page_manager.max_pages_per_group
+    self._page_map_dev = torch.zeros(B, MP, dtype=i32, device=dev)
+    self._uploaded_map = None
+    # one pinned staging buffer per step: [token | group | pos | want] rows
+    self._desc_host = torch.zeros(4 * self._max_rows, dtype=i32).pin_memory()
+    self._desc_dev = torch.zeros(4 * self._max_rows, dtype=i32, device=dev)
+    self._sample_scratch = torch.zeros(5 * max(B, 1), dtype=torch.float32, device=dev)
+    self._first_token = torch.zeros(1, dtype=i32, device=dev)
+    self._first_log_prob = torch.zeros(1, dtype=torch.float32, device=dev)
+    self._logits = None
+    self._pools: List[Tuple[torch.Tensor, torch.Tensor]] = []
+    self._ws = None
+
+  def __del__(self):
+    try:
+      if self._handle:
+        self.lib.mtx_layered_destroy(self._handle)
+    except Exception:  # pragma: no cover - interpreter shutdown
+      pass
+
+  # -- weights ------------------------------------------------------------------------------------
+
+  def load_params(self, params: Any = None, rng: Any = None, on_device_init: bool = False, norm_jitter: float = 0.0) -> LayeredParams:
+    """`params`: the design's tensors by their stored names (``params.load_model_dir``), a LayeredParams, or None: the folder
+    ``config.model_dir`` if set, else random weights (made on the device with ``on_device_init``)."""
+    cfg = self.config
+    if isinstance(params, LayeredParams):
+      lp = params
+    else:
+      design = design_module(cfg)
+      if params is None:
+        if cfg.model_dir:
+          params = params_lib.load_model_dir(cfg.model_dir)
+        else:
+          params = design.random_tensors(cfg, seed=int(cfg.init_weights_seed), device=self.device if on_device_init else "cpu")
+      lp = LayeredParams(design.model_plan(cfg, params), cfg, self.device)
+    if lp.float32 != (cfg.dtype == "float32"):
+      raise ValueError("these LayeredParams were packed for another dtype")
+    self._create(lp)
+    self._params = lp
+    return lp
+
+  def _create(self, lp: LayeredParams) -> None:
+    cfg, dev = self.config, self.device
+    if self._handle:
+      self.lib.mtx_layered_destroy(self._handle)
+      self._handle = ctypes.c_void_p()
+    pm = self.page_manager
+    ct = torch.float32 if lp.float32 else torch.bfloat16
+    self._pools = []
+    descs = (_lib.LayerDesc * len(lp.layers))()
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    for i, l in enumerate(lp.layers):
+      # (+1 page of slack behind the pool: the tensor-core attention reads whole 16-byte chunks of a row)
+      kp = torch.zeros(l["kv_heads"], pm.num_pages, pm.tokens_per_page, l["dim"], dtype=ct, device=dev)
+      vp = torch.zeros(l["kv_heads"], pm.num_pages, pm.tokens_per_page, l["vdim"], dtype=ct, device=dev)
+      self._pools.append((kp, vp))
+      d = descs[i]
+      d.mixer = _MIXERS[l["mixer"]]
+      for k in ("heads", "kv_heads", "dim", "vdim", "window", "value_mix", "ff"):
+        setattr(d, k, int(l[k]))
+      for k in ("scale", "softcap", "value_lambda", "gain1", "gain2"):
+        setattr(d, k, float(l[k]))
+      for k in ("wqkv", "bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk", "wo", "w_gate_up", "w_down"):
+        setattr(d, k, ptr(l[k]))
+      d.k_pages, d.v_pages = kp.data_ptr(), vp.data_ptr()
+    c = _lib.LayeredConfig(
+        num_layers=len(lp.layers), width=int(cfg.emb_dim), vocab=int(cfg.vocab_size), float32=1 if lp.float32 else 0,
+        max_rows=self._max_rows, max_want=self._max_rows, num_groups=self.max_concurrent_decodes, num_pages=pm.num_pages,
+        tokens_per_page=pm.tokens_per_page, max_pages_per_group=pm.max_pages_per_group, eps=float(cfg.normalization_layer_epsilon),
+        embed_scale=lp.embed_scale, final_gain=lp.final_gain, embedding=lp.embedding.data_ptr(), head=lp.head.data_ptr())
+    _lib.check(self.lib.mtx_layered_create(ctypes.byref(c), descs, ctypes.byref(self._handle)))
+    ws = int(self.lib.mtx_layered_workspace_bytes(self._handle))
+    self._ws = torch.empty(ws + 1024, dtype=torch.uint8, device=dev)
+    base = (self._ws.data_ptr() + 1023) // 1024 * 1024
+    _lib.check(self.lib.mtx_layered_bind(self._handle, ctypes.c_void_p(base), ws))
+    self._logits_buf = torch.zeros(self._max_rows, int(cfg.vocab_size), dtype=torch.float32, device=dev)
+
+  def _require_params(self, params) -> None:
+    if self._params is None or (params is not None and params is not self._params):
+      raise ValueError("pass the params returned by this engine's load_params")
+
+  # -- state --------------------------------------------------------------------------------------
+
+  def init_decode_state(self, rng: Any = None) -> dict:
+    for t in (self._tokens, self._next_pos, self._generated, self._active, self._result):
+      t.zero_()
+    self._rng_state[0:1].zero_()
+    self._seed(rng)
+    self.page_state = self.page_manager.get_initial_page_state()
+    self._uploaded_map = None
+    B, V = self.max_concurrent_decodes, int(self.config.vocab_size)
+    self._logits = torch.zeros(B, 1, V, dtype=torch.float32, device=self.device)
+    self._state = {
+        "logits": self._logits,
+        "cache": {"key_pages": [p[0] for p in self._pools], "value_pages": [p[1] for p in self._pools]},
+        "next_pos": self._next_pos,
+        "generated_tokens": self._generated,
+        "tokens": self._tokens,
+    }
+    return self._state
+
+  def _upload_page_map(self) -> None:
+    ps = self.page_state
+    if ps.page_map is not self._uploaded_map:
+      self._page_map_dev.copy_(torch.from_numpy(ps.page_map))
+      self._uploaded_map = ps.page_map
+
+  def _upload_page_state(self) -> None:  # (MaxEngine.release_pages calls it for device-resident page states; nothing to do here)
+    return
+
+  def release_pages(self, slot: int) -> None:
+    """The slot's pages go back to the pool.  Its row of the page map is cleared too, so that the row an empty slot still
+    contributes to a decode step lands on page 0 (never handed out) and not on a page somebody else owns by then."""
+    slot = int(slot)
+    ps = self.page_manager.release_pages(page_state=self.page_state, page_group_id=slot)
+    page_map = ps.page_map.copy()
+    page_map[slot] = 0
+    self.page_state = ps.replace(page_map=page_map)
+    self._active[slot].zero_()
+    self._next_pos[slot].zero_()
+
+  # -- the ragged step ----------------------------------------------------------------------------
+
+  def _run(self, rows: int, token_ptr: int, group_ptr: int, pos_ptr: int, n_want: int, want_ptr: int, logits: Optional[torch.Tensor]) -> None:
+    b = _lib.RaggedBatch(rows=rows, token=token_ptr, group=group_ptr, pos=pos_ptr, page_map=self._page_map_dev.data_ptr(), n_want=n_want,
+                         want_rows=want_ptr if n_want else None, logits=logits.data_ptr() if n_want else None)
+    _lib.check(self.lib.mtx_layered_step(self._handle, ctypes.byref(b), self._stream()))
+
+  def step(self, entries: Sequence[Tuple[int, Sequence[int], Sequence[int]]]) -> torch.Tensor:
+    """One mixed batch.  `entries`: (slot, the sequence's next tokens, indices among them whose logits are wanted).  Every
+    sequence grows by its tokens (pages are reserved as needed; ValueError when the pool is exhausted); returns the wanted
+    logits [n, vocab] (fp32, on the device) in the order of the entries.  Steps longer than max_step_rows run in slices."""
+    self._require_params(None)
+    B, V = self.max_concurrent_decodes, int(self.config.vocab_size)
+    tok, grp, pos, want = [], [], [], []
+    ps = self.page_state
+    seen = set()
+    for slot, tokens, wanted in entries:
+      slot = int(slot)
+      if not 0 <= slot < B or slot in seen:
+        raise ValueError(f"slot {slot}: outside [0, {B}) or twice in one step")
+      seen.add(slot)
+      n = len(tokens)
+      if n == 0:
+        continue
+      start = int(ps.sequence_lengths[slot])
+      new = self.page_manager.extend_pages(ps, slot, start + n)
+      if int(new.sequence_lengths[slot]) != start + n:
+        raise ValueError(f"slot {slot}: the page pool cannot hold {start + n} tokens")
+      ps = new
+      base = len(tok)
+      tok.extend(int(t) for t in tokens)
+      grp.extend([slot] * n)
+      pos.extend(range(start, start + n))
+      for w in wanted:
+        if not 0 <= int(w) < n:
+          raise ValueError(f"slot {slot}: wanted index {w} outside its {n} tokens")
+        want.append(base + int(w))
+    self.page_state = ps
+    self._upload_page_map()
+    rows = len(tok)
+    out = torch.empty(len(want), V, dtype=torch.float32, device=self.device)
+    if rows == 0:
+      return out
+    R = self._max_rows
+    done_want = 0
+    for lo in range(0, rows, R):
+      hi = min(rows, lo + R)
+      n = hi - lo
+      w = [x - lo for x in want if lo <= x < hi]
+      host = self._desc_host
+      host[0:n] = torch.tensor(tok[lo:hi], dtype=torch.int32)
+      host[R : R + n] = torch.tensor(grp[lo:hi], dtype=torch.int32)
+      host[2 * R : 2 * R + n] = torch.tensor(pos[lo:hi], dtype=torch.int32)
+      if w:
+        host[3 * R : 3 * R + len(w)] = torch.tensor(w, dtype=torch.int32)
+      if lo:
+        torch.cuda.current_stream(self.device).synchronize()  # the previous slice has read the staging buffer
+      self._desc_dev.copy_(host, non_blocking=True)
+      p = self._desc_dev.data_ptr()
+      dst = out[done_want : done_want + len(w)]
+      self._run(n, p, p + 4 * R, p + 8 * R, len(w), p + 12 * R, dst)
+      done_want += len(w)
+    torch.cuda.current_stream(self.device).synchronize()  # the pinned staging buffer is free again when step returns
+    return out
+
+  def _sample(self, logits: torch.Tensor, rows: int, token_out: torch.Tensor, log_prob_out: Optional[torch.Tensor], row_offset: int) -> None:
+    cfg = self.config
+    _lib.check(self.lib.mtx_sample_rows(
+        ctypes.c_void_p(logits.data_ptr()), rows, int(logits.stride(0)), int(cfg.vocab_size), _lib.SAMPLING[cfg.decode_sampling_strategy],
+        int(cfg.decode_sampling_top_k), float(cfg.decode_sampling_nucleus_p), float(cfg.decode_sampling_temperature),
+        ctypes.c_void_p(self._rng_state.data_ptr()), row_offset, ctypes.c_void_p(self._sample_scratch.data_ptr()),
+        ctypes.c_void_p(token_out.data_ptr()), ctypes.c_void_p(log_prob_out.data_ptr()) if log_prob_out is not None else None, self._stream()))
+    self._rng_state[0:1] += 1  # every draw has its own noise
+
+  # -- the engine API -----------------------------------------------------------------------------
+
+  def prefill(self, *, params: Any = None, padded_tokens: Any, true_length: int, existing_prefix: Any = None, images: Any = None,
+              sampler: Any = None, rng: Any = None, request_id: Any = None, slot: Optional[int] = None, return_prompt_logp: bool = False):
+    """maxengine.py:533-574 for one sequence; the rows go straight into the pages of `slot` (required).  `existing_prefix`
+    (chunked prefill): the slot already holds that prefix and grows."""
+    self._require_params(params)
+    if slot is None:
+      raise ValueError("a layered model prefills into the pages of a slot: pass slot=")
+    if return_prompt_logp:
+      raise NotImplementedError("return_prompt_logp is outside the decode path")
+    self._seed(rng)
+    slot, true_length = int(slot), int(true_length)
+    toks = torch.as_tensor(padded_tokens).reshape(-1)
+    if true_length < 1 or true_length > toks.numel():
+      raise ValueError(f"true_length={true_length} for {toks.numel()} padded tokens")
+    start = 0
+    if existing_prefix is not None:
+      start = int(torch.as_tensor(existing_prefix.common_prefix_tokens).reshape(-1).numel())
+      if int(self.page_state.sequence_lengths[slot]) != start:
+        raise ValueError(f"slot {slot} holds {int(self.page_state.sequence_lengths[slot])} tokens, the prefix has {start}")
+    else:
+      self.release_pages(slot)
+    if start + true_length >= int(self.config.max_target_length):
+      raise ValueError(f"{start + true_length} prompt tokens leave no room to decode (max_target_length={self.config.max_target_length})")
+    logits = self.step([(slot, toks[:true_length].tolist(), [true_length - 1])])
+    self._sample(logits, 1, self._first_token, self._first_log_prob if self.config.return_log_prob else None, 0x40000000)
+    first = self._first_token.clone().reshape(1, 1)
+    n = start + true_length
+    prefix = {
+        "logits": logits.reshape(1, 1, -1),
+        "cache": {"slot": slot, "prefill_length": n},  # the keys and values are in the slot's pages already
+        "next_pos": torch.full((1, 1), n, dtype=torch.int32, device=self.device),
+        "generated_tokens": torch.zeros((1, 1), dtype=torch.int32, device=self.device),
+        "tokens": first,
+    }
+    data = torch.cat((first, torch.ones_like(first), torch.zeros_like(first)), dim=1)
+    lp = self._first_log_prob.clone().reshape(1, 1) if self.config.return_log_prob else None
+    return prefix, ResultTokens(data=data, log_prob=lp)
+
+  def insert(self, prefix: dict, decode_state: dict, slot: int, request_id: Any = None) -> dict:
+    """maxengine.py:1166-1192.  The prefix lives in the pages of the slot it was prefilled into: that must be `slot`."""
+    if decode_state is not self._state:
+      raise ValueError("decode_state must be the dict returned by this engine's init_decode_state (it is donated)")
+    slot = int(slot)
+    if int(prefix["cache"]["slot"]) != slot:
+      raise ValueError(f"this prefix was prefilled into slot {prefix['cache']['slot']}, not {slot}")
+    self._next_pos[slot].copy_(prefix["next_pos"][0])
+    self._generated[slot].copy_(prefix["generated_tokens"][0])
+    self._tokens[slot].copy_(prefix["tokens"][0])
+    self._active[slot].fill_(1)
+    self._logits[slot].copy_(prefix["logits"][0])
+    return decode_state
+
+  def bulk_insert(self, prefix: dict, decode_state: dict, slots: list) -> dict:
+    raise NotImplementedError("a paged prefix belongs to one slot")
+
+  def _decode_rows(self) -> None:
+    """One row per slot: token and position from the device state, the slot's pages grown by one token on the host."""
+    B = self.max_concurrent_decodes
+    ps = self.page_manager.update_decode_pages(self.page_state)
+    grew = ps.has_active_page & (ps.num_pages_used * self.page_manager.tokens_per_page < ps.sequence_lengths)
+    if grew.any():
+      raise ValueError(f"the page pool is exhausted: slots {np.flatnonzero(grew).tolist()} cannot grow")
+    self.page_state = ps
+    self._upload_page_map()
+    self._run(B, self._tokens.data_ptr(), self._slot_ids.data_ptr(), self._next_pos.data_ptr(), B, self._slot_ids.data_ptr(), self._logits)
+    self._sample(self._logits.view(B, -1), B, self._tokens, self._log_prob, 0)
+    # bookkeeping of maxengine.py:913-928 for the occupied slots (empty ones stay at position 0 on page 0)
+    self._next_pos.add_(self._active)
+    self._generated.add_(self._active)
+    self._result[:, 0:1].copy_(self._tokens)
+    self._result[:, 1:2].copy_(self._active)
+    self._result[:, 2:3].copy_(self._generated)
+
+  def generate(self, params: Any, decode_state: dict, sampler: Any = None, rng: Any = None):
+    if decode_state is not self._state:
+      raise ValueError("decode_state must be the dict returned by this engine's init_decode_state (it is donated)")
+    self._require_params(params)
+    self._seed(rng)
+    self._decode_rows()
+    return decode_state, ResultTokens(data=self._result.clone(), log_prob=self._log_prob.clone() if self._log_prob is not None else None)
+
+  def generate_to_host(self, params: Any, decode_state: dict, host_result: torch.Tensor, host_tokens: Optional[torch.Tensor] = None,
+                       host_log_prob: Optional[torch.Tensor] = None, sync: bool = False):
+    if decode_state is not self._state:
+      raise ValueError("decode_state must be the dict returned by this engine's init_decode_state (it is donated)")
+    self._require_params(params)
+    if host_tokens is not None:
+      self._tokens.copy_(host_tokens.reshape(self._tokens.shape), non_blocking=True)
+    self._decode_rows()
+    host_result.copy_(self._result, non_blocking=True)
+    if host_log_prob is not None and self._log_prob is not None:
+      host_log_prob.copy_(self._log_prob, non_blocking=True)
+    if sync:
+      torch.cuda.current_stream(self.device).synchronize()
+    return decode_state, ResultTokens(data=host_result, log_prob=host_log_prob)

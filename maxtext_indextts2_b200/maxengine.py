@@ -243,6 +243,18 @@ def random_device_params(config, device, seed: int = 0, norm_jitter: float = 0.0
 class MaxEngine:
   """The reference's ``MaxEngine`` for one B200 (one process per GPU)."""
 
+  def __new__(cls, config, *args, **kwargs):
+    """The model registry of the engine: a layered design (pyconfig.LAYERED_BLOCKS) is served by LayeredEngine, the same API
+    over the layered device engine; llama2 / gemma3 by this class."""
+    if cls is MaxEngine:
+      from . import pyconfig
+
+      if config.decoder_block in pyconfig.LAYERED_BLOCKS:
+        from . import layered_engine
+
+        return object.__new__(layered_engine.LayeredEngine)
+    return object.__new__(cls)
+
   def __init__(self, config, devices: Any = None, use_cuda_graph: bool = True, vocab_shard: Optional[tuple] = None,
                gather: Any = None):
     """`vocab_shard` = (rank, world) and `gather` (candidates [5,B] -> [world,5,B]) default to the

@@ -99,6 +99,41 @@ def _reserve_pages_for_group(state: PageState, group: int, true_length: int, tok
   )
 
 
+def _extend_pages_for_group(state: PageState, group: int, new_length: int, tokens_per_page: int, max_pages_per_group: int) -> PageState:
+  """Grow the group to `new_length` tokens, keeping the pages it has: the lowest free pages are appended to its row of the page
+  map, or nothing changes when the pool (or the row) cannot hold them.  With a length the group already covers only the length
+  fields move.  This is what a prompt that arrives in portions needs: `_reserve_pages_for_group` wants the final length at once."""
+  needed = (new_length + tokens_per_page - 1) // tokens_per_page
+  used = int(state.num_pages_used[group])
+  extra = max(0, needed - used)
+  free = np.flatnonzero(state.page_status[1:] == 0) + 1
+  if needed > max_pages_per_group or free.size < extra:
+    return state
+  status, page_map, n_used = state.page_status, state.page_map, state.num_pages_used
+  if extra:
+    take = free[:extra].astype(np.int32)
+    status, page_map, n_used = status.copy(), page_map.copy(), n_used.copy()
+    status[take] = 1
+    page_map[group, used:needed] = take
+    n_used[group] = needed
+
+  def with_value(a, value):
+    a = a.copy()
+    a[group] = value
+    return a
+
+  last = page_map[group, needed - 1] if needed else 0
+  return state.replace(
+      page_status=status,
+      page_map=page_map,
+      num_pages_used=n_used,
+      sequence_lengths=with_value(state.sequence_lengths, new_length),
+      active_page=with_value(state.active_page, last),
+      has_active_page=with_value(state.has_active_page, True),
+      active_page_position=with_value(state.active_page_position, new_length % tokens_per_page),
+  )
+
+
 def _update_decode_pages_global(state: PageState, tokens_per_page: int, max_pages_per_group: int) -> PageState:
   """page_manager.py:332-412: one more token for every active group; groups that crossed a page boundary get the lowest
   free page, in group order, while free pages last."""
@@ -159,6 +194,15 @@ class PageManager:
       raise ValueError(f"PageManager: true_length ({true_length}) out of range (0, {self.max_target_length}]")
     released = _release_pages_for_group(page_state, page_group_id)
     return _reserve_pages_for_group(released, page_group_id, int(true_length), self.tokens_per_page, self.max_pages_per_group)
+
+  def extend_pages(self, page_state: PageState, page_group_id: int, new_length: int) -> PageState:
+    """Not in the reference: the group grows to `new_length` tokens and keeps what it holds (a prompt fed in portions, several
+    tokens decoded at once).  Returns the state unchanged (compare `sequence_lengths`) when the pool cannot hold it."""
+    if page_group_id < 0 or page_group_id >= self.max_page_groups:
+      raise ValueError(f"PageManager: page_group_id ({page_group_id}) out of range [0, {self.max_page_groups})")
+    if new_length < int(page_state.sequence_lengths[page_group_id]) or new_length > self.max_target_length:
+      raise ValueError(f"PageManager: new_length ({new_length}) out of range [{int(page_state.sequence_lengths[page_group_id])}, {self.max_target_length}]")
+    return _extend_pages_for_group(page_state, page_group_id, int(new_length), self.tokens_per_page, self.max_pages_per_group)
 
   def update_decode_pages(self, page_state: PageState) -> PageState:
     """:538-563."""

@@ -198,3 +198,40 @@ def param_count(config) -> dict:
       "logits": 0 if config.logits_via_embedding else E * V,
       "embedding": V * E,
   }
+
+
+_SAFETENSORS_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F64": torch.float64, "I32": torch.int32,
+                       "I64": torch.int64, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8, "BOOL": torch.bool}
+
+
+def load_safetensors(path: str) -> dict:
+  """name -> CPU tensor of a .safetensors file: an 8-byte little-endian header length, that many bytes of JSON
+  (name -> dtype, shape, data_offsets relative to the end of the header), then the raw little-endian data."""
+  import json
+
+  with open(path, "rb") as f:
+    raw = f.read()
+  n = int.from_bytes(raw[:8], "little")
+  header = json.loads(raw[8 : 8 + n].decode("utf-8"))
+  data = memoryview(raw)[8 + n :]
+  out = {}
+  for name, meta in header.items():
+    if name == "__metadata__":
+      continue
+    if meta["dtype"] not in _SAFETENSORS_DTYPES:
+      raise ValueError(f"{path}: tensor {name!r} has the unsupported dtype {meta['dtype']}")
+    lo, hi = meta["data_offsets"]
+    dt = _SAFETENSORS_DTYPES[meta["dtype"]]
+    shape = tuple(int(s) for s in meta["shape"])
+    count = int(np.prod(shape)) if shape else 1
+    if hi - lo != count * torch.empty((), dtype=dt).element_size():
+      raise ValueError(f"{path}: tensor {name!r}: {hi - lo} bytes for shape {shape} of {meta['dtype']}")
+    out[name] = torch.frombuffer(bytearray(data[lo:hi]), dtype=dt).reshape(shape) if count else torch.empty(shape, dtype=dt)
+  return out
+
+
+def load_model_dir(model_dir: str) -> dict:
+  """The tensors of a model folder (model.safetensors), by their stored names."""
+  import os
+
+  return load_safetensors(os.path.join(model_dir, "model.safetensors"))

@@ -34,6 +34,10 @@ _MAX_PREFIX = "M_"
 _VALID_ATTENTION = ("autoselected", "dot_product", "flash", "cudnn_flash_te", "cudnn_flash_jax", "paged")
 _VALID_SAMPLING = ("greedy", "weighted", "nucleus", "topk")
 _VALID_AXIS_ORDER = ("0,1,2,3", "0,2,1,3")
+# Designs whose layers are listed one by one (`layer_specs`) and run on the layered engine (layered_engine.py), keyed by
+# decoder_block; ARCHITECTURES maps the "architecture" of a model folder's config.json to the block.
+LAYERED_BLOCKS = ("kifusun",)
+ARCHITECTURES = {"Kifusun": "kifusun"}
 
 
 def _string_to_bool(s: str) -> bool:
@@ -100,7 +104,34 @@ class HyperParameters:
     return dict(object.__getattribute__(self, "_keys"))
 
 
+def _validate_layered(keys: dict) -> None:
+  """A layered design: paged bf16 / fp32 cache, its layers checked by the design's own module."""
+  if keys["dtype"] not in ("bfloat16", "float32"):
+    raise ValueError("dtype must be bfloat16 or float32 for a layered model")
+  if keys["attention"] != "paged":
+    raise ValueError("a layered model is served from the paged cache: attention=paged")
+  if keys["quantize_kvcache"] or keys["quantization"] not in ("", None) or int(keys["vocab_parallelism"]) != 1:
+    raise ValueError("a layered model runs with an unquantised cache, unquantised weights and vocab_parallelism=1")
+  if int(keys["pagedattn_tokens_per_page"]) < 1 or int(keys["pagedattn_num_pages"]) <= 1:
+    raise ValueError("pagedattn_tokens_per_page must be positive and pagedattn_num_pages greater than 1")
+  if int(keys["max_step_rows"]) < 1:
+    raise ValueError("max_step_rows must be positive")
+  if not keys["layer_specs"]:
+    raise ValueError("a layered model needs layer_specs (pyconfig.from_model_dir reads them from config.json)")
+  if keys["decoder_block"] == "kifusun":
+    from . import kifusun
+
+    kifusun.validate_layer_specs(keys["layer_specs"])
+
+
 def _validate(keys: dict) -> None:
+  if keys["decoder_block"] in LAYERED_BLOCKS:
+    if keys["attention"] not in _VALID_ATTENTION:
+      raise ValueError("Invalid attention kernel was passed. Valid options ", _VALID_ATTENTION)
+    if keys["decode_sampling_strategy"] not in _VALID_SAMPLING:
+      raise ValueError(f"Sampling algorithm={keys['decode_sampling_strategy']!r} not supported!")
+    _validate_layered(keys)
+    return
   if keys["attention"] not in _VALID_ATTENTION:
     raise ValueError("Invalid attention kernel was passed. Valid options ", _VALID_ATTENTION)
   if keys["compute_axis_order"] not in _VALID_AXIS_ORDER:
@@ -119,7 +150,7 @@ def _validate(keys: dict) -> None:
   if keys["quantization"] not in ("", None):
     raise ValueError("quantization must be '' on this decode path (bf16 weights only)")
   if keys["decoder_block"] not in ("llama2", "gemma3"):
-    raise ValueError(f"decoder_block={keys['decoder_block']!r}: the llama2 and gemma3 blocks are on this path")
+    raise ValueError(f"decoder_block={keys['decoder_block']!r}: the llama2 and gemma3 blocks (and the layered designs {LAYERED_BLOCKS}) are on this path")
   if keys["dtype"] != "bfloat16":
     raise ValueError("dtype must be bfloat16 on this path")
   if keys["rope_type"] != "default":
@@ -145,6 +176,8 @@ def _validate(keys: dict) -> None:
       raise ValueError("only mlp_activations=[silu, linear] is on this path")
     if keys["use_post_attn_norm"] or keys["use_post_ffw_norm"] or keys["sliding_window_size"]:
       raise ValueError("use_post_attn_norm / use_post_ffw_norm / sliding_window_size belong to the gemma3 block")
+  if keys["layer_specs"] or keys["model_dir"]:
+    raise ValueError("layer_specs / model_dir belong to the layered designs")
   if keys["max_target_length"] <= keys["max_prefill_predict_length"]:
     # inference/kvcache.py:408-412
     raise ValueError(
@@ -235,3 +268,26 @@ def initialize(argv=None, **kwargs) -> HyperParameters:
 
   _validate(keys)
   return HyperParameters(keys)
+
+
+def from_model_dir(model_dir: str, **overrides) -> HyperParameters:
+  """The config of a model folder (config.json + model.safetensors): the design is chosen by config.json's "architecture"
+  (ARCHITECTURES), its sizes and constants become the keys the engine reads; `overrides` are ordinary keys (dtype,
+  per_device_batch_size, pagedattn_*, max_target_length, sampling ...)."""
+  import json
+
+  with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
+    model = json.load(f)
+  arch = model.get("architecture")
+  if arch not in ARCHITECTURES:
+    raise ValueError(f"config.json names the architecture {arch!r}; known: {sorted(ARCHITECTURES)}")
+  block = ARCHITECTURES[arch]
+  if block == "kifusun":
+    from . import kifusun
+
+    keys = kifusun.config_keys(model)
+  keys.update(model_dir=os.path.abspath(model_dir), decoder_block=block, attention="paged", scan_layers=False, weight_dtype="bfloat16")
+  keys.update(overrides)
+  if "max_prefill_predict_length" not in overrides:  # any prompt that fits the sequence
+    keys["max_prefill_predict_length"] = int(keys.get("max_target_length", _load_yaml(BASE_YML)["max_target_length"])) - 1
+  return initialize(None, **keys)
