@@ -59,9 +59,9 @@ def validate_layer_specs(specs: List[dict]) -> None:
     if int(m["mask"]["size"]) < 1:
       raise ValueError(f"layer {i}: mask.size must be positive")
     if m.get("v_mix"):
-      size = int(m["kv_heads"]) * int(m["vdim"])
+      size = (int(m["kv_heads"]), int(m["vdim"]))
       if shared is not None and size != shared:
-        raise ValueError(f"layer {i}: value mixing needs kv_heads * vdim = {shared} as in the first mixing layer")
+        raise ValueError(f"layer {i}: value mixing needs (kv_heads, vdim) = {shared} as in the first mixing layer")
       shared = size if shared is None else shared
     ff = l.get("mlp")
     if ff is not None and ff.get("kind", "dense") not in FF_KINDS:

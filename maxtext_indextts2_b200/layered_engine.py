@@ -78,6 +78,8 @@ class LayeredParams:
 class LayeredEngine(MaxEngine):
   """``MaxEngine(config)`` returns this class when ``config.decoder_block`` is a layered design."""
 
+  prompt_and_decode_share_pages = True  # no prefill segment + AR ring: a sequence is one page group that grows
+
   def __init__(self, config, devices: Any = None, use_cuda_graph: bool = True, vocab_shard: Optional[tuple] = None, gather: Any = None):
     if vocab_shard is not None or int(config.vocab_parallelism) != 1:
       raise ValueError("a layered model runs with vocab_parallelism=1")

@@ -62,7 +62,12 @@ class OfflineEngine:
     sequences finish.  Returns the completions in prompt order."""
     P = self.engine.max_prefill_length
     R = self.config.max_target_length - P
-    if max_decode_length > R:
+    if getattr(self.engine, "prompt_and_decode_share_pages", False):
+      # a layered engine has no separate AR ring: a sequence grows in its page group up to max_target_length
+      longest = max((len(p) for p in prompts), default=0)
+      if longest + max_decode_length > self.config.max_target_length:
+        raise ValueError(f"a prompt of {longest} tokens plus max_decode_length {max_decode_length} exceeds max_target_length {self.config.max_target_length}")
+    elif max_decode_length > R:
       raise ValueError(f"max_decode_length {max_decode_length} exceeds the AR ring of {R} rows")
     pending = list(range(len(prompts)))[::-1]
     slot_to_id: List[Optional[int]] = [None] * self.slots

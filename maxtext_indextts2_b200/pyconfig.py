@@ -270,14 +270,10 @@ def initialize(argv=None, **kwargs) -> HyperParameters:
   return HyperParameters(keys)
 
 
-def from_model_dir(model_dir: str, **overrides) -> HyperParameters:
-  """The config of a model folder (config.json + model.safetensors): the design is chosen by config.json's "architecture"
-  (ARCHITECTURES), its sizes and constants become the keys the engine reads; `overrides` are ordinary keys (dtype,
-  per_device_batch_size, pagedattn_*, max_target_length, sampling ...)."""
-  import json
-
-  with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
-    model = json.load(f)
+def from_model_dict(model: dict, **overrides) -> HyperParameters:
+  """The config of a model given as the dict its config.json holds: the design is chosen by "architecture" (ARCHITECTURES), its
+  sizes and constants become the keys the engine reads; `overrides` are ordinary keys (dtype, per_device_batch_size,
+  pagedattn_*, max_target_length, sampling ...)."""
   arch = model.get("architecture")
   if arch not in ARCHITECTURES:
     raise ValueError(f"config.json names the architecture {arch!r}; known: {sorted(ARCHITECTURES)}")
@@ -286,8 +282,17 @@ def from_model_dir(model_dir: str, **overrides) -> HyperParameters:
     from . import kifusun
 
     keys = kifusun.config_keys(model)
-  keys.update(model_dir=os.path.abspath(model_dir), decoder_block=block, attention="paged", scan_layers=False, weight_dtype="bfloat16")
+  keys.update(decoder_block=block, attention="paged", scan_layers=False, weight_dtype="bfloat16")
   keys.update(overrides)
   if "max_prefill_predict_length" not in overrides:  # any prompt that fits the sequence
     keys["max_prefill_predict_length"] = int(keys.get("max_target_length", _load_yaml(BASE_YML)["max_target_length"])) - 1
   return initialize(None, **keys)
+
+
+def from_model_dir(model_dir: str, **overrides) -> HyperParameters:
+  """The config of a model folder (config.json + model.safetensors; ``params.load_model_dir`` reads the weights)."""
+  import json
+
+  with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
+    model = json.load(f)
+  return from_model_dict(model, model_dir=os.path.abspath(model_dir), **overrides)

@@ -149,7 +149,7 @@ class KifusunRef:
     return self.head(x)
 
 
-def random_model(config: dict, seed: int = 0) -> dict:
+def random_model(config: dict, seed: int = 0, bias_rows: int = 10) -> dict:
   """Random bf16 weights with the design's tensor names for `config` (a dict with the keys of its config.json)."""
   g = torch.Generator().manual_seed(seed)
   E, V = int(config["width"]), int(config["vocab"])
@@ -159,7 +159,7 @@ def random_model(config: dict, seed: int = 0) -> dict:
   for i, l in enumerate(config["layers"]):
     m, p = l["mixer"], f"l{i}."
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    rows = int(m.get("bias_rows", 16))
+    rows = bias_rows
     t[p + "norm1"] = (0.7 + 0.2 * torch.randn((), generator=g)).to(bf)
     t[p + "mix.q"], t[p + "mix.q.b"] = rn(H * d, E, std=1.0 / math.sqrt(E)), rn(H * d, std=0.1)
     t[p + "mix.k"], t[p + "mix.k.b"] = rn(G * d, E, std=1.0 / math.sqrt(E)), rn(G * d, std=0.1)
@@ -179,13 +179,13 @@ def random_model(config: dict, seed: int = 0) -> dict:
   return t
 
 
-def small_config(layers=3, width=48, vocab=61, heads=4, kv_heads=2, dim=24, vdim=16, window=7, ff=40, bias_rows=10, bias_max=40,
+def small_config(layers=3, width=48, vocab=61, heads=4, kv_heads=2, dim=24, vdim=16, window=7, ff=40, bias_max=40,
                  softcap=30.0, v_mix=(True, True, True), mlp=(True, False, True), eps=1e-5, embed_scale=3.0):
   """A config dict in the layout of the design's config.json, with small sizes."""
   ls = []
   for i in range(layers):
     ls.append({"type": "attention",
                "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": window}, "scale": dim**-0.5,
-                         "softcap": softcap, "bias_max": bias_max, "v_mix": bool(v_mix[i % len(v_mix)]), "bias_rows": bias_rows},
+                         "softcap": softcap, "bias_max": bias_max, "v_mix": bool(v_mix[i % len(v_mix)])},
                "mlp": {"kind": "dense", "ff": ff} if mlp[i % len(mlp)] else None})
   return {"architecture": "Kifusun", "vocab": vocab, "width": width, "embedding": {"scale": embed_scale}, "norm": {"eps": eps}, "layers": ls}
