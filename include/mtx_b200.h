@@ -415,6 +415,10 @@ typedef struct {
   int32_t n_want;
   const int32_t* want_rows;    /* [n_want] rows whose logits are written */
   float* logits;               /* [n_want, vocab] */
+  /* Optional (n_tiles = 0: none): the rows cut into query tiles for the tensor-core mixer.  Tile t = rows [tile_row0[t],
+   * tile_row0[t + 1]): at most 16 rows of ONE group with consecutive positions; the tiles cover every row once. */
+  int32_t n_tiles;
+  const int32_t* tile_row0;    /* [n_tiles + 1] */
 } mtx_ragged_batch;
 
 typedef struct mtx_layered mtx_layered; /* opaque */

@@ -137,7 +137,8 @@ class RaggedBatch(ctypes.Structure):
   """mtx_ragged_batch."""
 
   _fields_ = [("rows", ctypes.c_int32), ("token", ctypes.c_void_p), ("group", ctypes.c_void_p), ("pos", ctypes.c_void_p),
-              ("page_map", ctypes.c_void_p), ("n_want", ctypes.c_int32), ("want_rows", ctypes.c_void_p), ("logits", ctypes.c_void_p)]
+              ("page_map", ctypes.c_void_p), ("n_want", ctypes.c_int32), ("want_rows", ctypes.c_void_p), ("logits", ctypes.c_void_p),
+              ("n_tiles", ctypes.c_int32), ("tile_row0", ctypes.c_void_p)]
 
 
 def sources() -> list[str]:

@@ -26,6 +26,8 @@ struct mtx_layered {
   // workspace carve-up
   float *x = nullptr, *y = nullptr, *qkv = nullptr, *v_shared = nullptr;
   void *xa = nullptr, *q = nullptr, *attn = nullptr, *act = nullptr, *wanted = nullptr, *obf = nullptr;
+  float* attn_part = nullptr;  // fp32 partial outputs of the attention's key splits: room for 2 * max_rows rows
+  size_t attn_part_rows = 0;
 };
 
 namespace {
@@ -33,7 +35,7 @@ namespace {
 size_t elem(const mtx_layered* e) { return e->cfg.float32 ? 4 : 2; }
 
 struct LWs {
-  size_t x, y, qkv, v_shared, xa, q, attn, act, wanted, obf, total;
+  size_t x, y, qkv, v_shared, xa, q, attn, act, wanted, obf, attn_part, total;
 };
 
 LWs layered_layout(const mtx_layered* e) {
@@ -57,6 +59,7 @@ LWs layered_layout(const mtx_layered* e) {
   L.act = take(R * (e->max_ff > 0 ? e->max_ff : 1) * es);
   L.wanted = take(W * c.width * es);
   L.obf = take(R * size_t(e->max_nqkv > c.width ? e->max_nqkv : c.width) * 2);  // bf16 output of a tcgen05 projection
+  L.attn_part = take(c.float32 ? 1024 : 2 * R * size_t(e->max_odim) * 4);
   L.total = off;
   return L;
 }
@@ -136,6 +139,47 @@ int pick_key_tile(const mtx_layer_desc& l) {
   return kt;
 }
 
+bool use_window_mma() {
+  static int on = env_int("MTX_WINDOW_MMA", 1);
+  return on != 0;
+}
+
+template <int HPW, int DVT>
+int launch_window_mma_t(const WindowAttnArgs<bf16>& wa, const WindowMmaExtra& x, size_t smem, cudaStream_t st) {
+  static size_t have = 0;  // per instantiation
+  if (smem > have) {
+    MTX_CUDA(cudaFuncSetAttribute(window_attention_mma_kernel<HPW, DVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    have = smem;
+  }
+  return launch(window_attention_mma_kernel<HPW, DVT>, dim3(x.n_tiles, x.splits), dim3(kWmmaThreads), smem, st, wa, x);
+}
+
+// the tensor-core mixer: (query tile, key split) work items, then the sum over the splits
+int launch_window_mma(mtx_layered* e, const WindowAttnArgs<bf16>& wa, const WindowMmaPlan& plan, const mtx_ragged_batch& b, cudaStream_t st) {
+  WindowMmaExtra x;
+  x.tile_row0 = b.tile_row0;
+  x.partial = e->attn_part;
+  x.n_tiles = b.n_tiles;
+  x.bn = plan.bn;
+  const int key_tiles = (wa.window + kWmmaRows - 1 + plan.bn - 1) / plan.bn;  // most key tiles a query tile can have
+  int splits = (2 * e->num_sms + b.n_tiles - 1) / b.n_tiles;
+  if (splits > key_tiles) splits = key_tiles;
+  if (size_t(splits) * wa.rows > e->attn_part_rows) splits = int(e->attn_part_rows / wa.rows);
+  if (splits < 1) splits = 1;
+  x.splits = splits;
+  int rc = MTX_ERR_UNSUPPORTED;
+  if (plan.hpw == 1 && plan.dvt == 8) rc = launch_window_mma_t<1, 8>(wa, x, plan.smem, st);
+  else if (plan.hpw == 1 && plan.dvt == 16) rc = launch_window_mma_t<1, 16>(wa, x, plan.smem, st);
+  else if (plan.hpw == 1 && plan.dvt == 32) rc = launch_window_mma_t<1, 32>(wa, x, plan.smem, st);
+  else if (plan.hpw == 2 && plan.dvt == 8) rc = launch_window_mma_t<2, 8>(wa, x, plan.smem, st);
+  else if (plan.hpw == 2 && plan.dvt == 16) rc = launch_window_mma_t<2, 16>(wa, x, plan.smem, st);
+  MTX_TRY(rc);
+  const long long per_split = (long long)wa.rows * wa.heads * wa.vdim;
+  long long blocks = (per_split / 2 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return launch(window_partial_sum_kernel, dim3(unsigned(blocks)), dim3(256), 0, st, (const float*)e->attn_part, wa.out, splits, per_split);
+}
+
 template <typename T>
 int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
   const mtx_layered_config& c = e->cfg;
@@ -197,8 +241,9 @@ int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
     wa.softcap = l.softcap;
     bool done = false;
     if constexpr (sizeof(T) == 2) {
-      if (window_mma_usable(wa) && rows >= window_mma_min_rows()) {
-        MTX_TRY(launch_window_mma(wa, st));
+      const WindowMmaPlan plan = window_mma_plan(H, G, l.dim, l.vdim);
+      if (plan.ok && b.n_tiles > 0 && b.tile_row0 != nullptr && use_window_mma()) {
+        MTX_TRY(launch_window_mma(e, wa, plan, b, st));
         done = true;
       }
     }
@@ -308,6 +353,8 @@ int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes) {
   e->act = base + L.act;
   e->wanted = base + L.wanted;
   e->obf = base + L.obf;
+  e->attn_part = reinterpret_cast<float*>(base + L.attn_part);
+  e->attn_part_rows = 2 * align_up(size_t(e->cfg.max_rows), 256);
   e->bound = true;
   return MTX_OK;
 }
@@ -317,6 +364,7 @@ int mtx_layered_step(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream strea
   if (b->rows < 1 || b->rows > e->cfg.max_rows) return fail(MTX_ERR_ARG, "rows = %d outside [1, %d]", b->rows, e->cfg.max_rows);
   if (b->n_want < 0 || b->n_want > e->cfg.max_want) return fail(MTX_ERR_ARG, "n_want = %d outside [0, %d]", b->n_want, e->cfg.max_want);
   if (!b->token || !b->group || !b->pos || !b->page_map || (b->n_want > 0 && (!b->want_rows || !b->logits))) return fail(MTX_ERR_ARG, "null batch array");
+  if (b->n_tiles < 0 || b->n_tiles > b->rows) return fail(MTX_ERR_ARG, "n_tiles = %d for %d rows", b->n_tiles, b->rows);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return e->cfg.float32 ? step_typed<float>(e, *b, st) : step_typed<bf16>(e, *b, st);
 }

@@ -1,14 +1,243 @@
-// Tensor-core arm of the windowed sigmoid attention (window_attention.cuh has the contract and the row kernel).
+// Tensor-core arm of the windowed sigmoid attention (window_attention.cuh has the contract and the row kernel), bf16 operands.
+//
+// Work item = (query tile, key split).  A query tile is up to 16 rows of ONE sequence with consecutive positions (a slice of a
+// prompt portion, or a single decoded token); the host passes the tile table.  Because the key weights are not normalised, the
+// partial outputs of the key splits simply add: every work item writes its fp32 partial [rows, H * dv] and a small kernel sums the
+// splits in a fixed order.  That is what lets 32 decode rows fill 148 SMs.
+//
+// One CTA of eight warps walks its keys in tiles of BN (32 or 64) staged in shared memory (K, V of all kv heads; rows fetched
+// through the page map one by one, so any page size works).  Per tile:
+//   S phase   warp w owns the keys [8w, 8w + 8) of the tile and ALL heads: S_g = Q_g K^T on mma.sync m16n8k16 (fp32 accumulators),
+//             then scale, soft cap, distance bias, head bias, sigmoid and the window mask on the accumulator registers -- a thread
+//             holds the same (row, key) element of every head, so the mixing of the heads' weights (an H x H matrix per element)
+//             is thread-local.  The mixed weights go to shared memory as bf16 [H][16][BN].
+//   PV phase  warp w owns HPW heads: out_h += P_h V_kv(h), V fragments through ldmatrix.trans.
+// Template: HPW heads per warp (H <= 8 * HPW), DVT = ceil(dv / 8) output tiles per head; HPW * DVT * 4 accumulator registers.
 #pragma once
 
 #include "window_attention.cuh"
 
 namespace mtx {
 
-template <typename T>
-inline bool window_mma_usable(const WindowAttnArgs<T>&) { return false; }
-inline int window_mma_min_rows() { return 1 << 30; }
-template <typename T>
-inline int launch_window_mma(const WindowAttnArgs<T>&, cudaStream_t) { return 0; }
+constexpr int kWmmaThreads = 256;
+constexpr int kWmmaRows = 16;
+
+struct WindowMmaExtra {
+  const int* tile_row0;  // [n_tiles + 1]
+  float* partial;        // [splits, rows, H * dv]
+  int n_tiles, splits, bn;
+};
+
+inline size_t window_mma_smem_bytes(int heads, int kv_heads, int dim, int vdim, int bn) {
+  return size_t(2) * (size_t(kWmmaRows) * (heads * dim + 8) + size_t(kv_heads) * bn * (dim + 8) + size_t(kv_heads) * bn * (vdim + 8) +
+                      size_t(heads) * kWmmaRows * (bn + 8)) +
+         sizeof(float) * (size_t(heads) * heads + heads) + sizeof(int) * 64;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int HPW, int DVT>
+__global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(const WindowAttnArgs<bf16> a, const WindowMmaExtra x) {
+  constexpr int HMAX = 8 * HPW;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = a.heads, G = a.kv_heads, d = a.dim, dv = a.vdim, BN = x.bn, rep = H / G;
+  const int QP = H * d + 8, KP = d + 8, VP = dv + 8, PP = BN + 8;
+  bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [16][QP]
+  bf16* sK = sQ + kWmmaRows * QP;                     // [G][BN][KP]
+  bf16* sV = sK + G * BN * KP;                        // [G][BN][VP]
+  bf16* sP = sV + G * BN * VP;                        // [H][16][PP]
+  float* sTalk = reinterpret_cast<float*>(sP + H * kWmmaRows * PP);  // [H][H]
+  float* sPb = sTalk + H * H;                         // [H]
+  int* sRow = reinterpret_cast<int*>(sPb + H);        // [BN] cache row of each key of the tile (-1: none)
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, t4 = lane & 3;
+  griddep_wait();
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int r0 = x.tile_row0[tile], nrows = x.tile_row0[tile + 1] - r0;
+  const int grp = a.group[r0], p0 = a.pos[r0];
+  const int klo = p0 - a.window + 1 > 0 ? p0 - a.window + 1 : 0, khi = p0 + nrows - 1;
+  const int n_kt = (khi - klo + BN) / BN, per = (n_kt + x.splits - 1) / x.splits;
+  const int kt_lo = split * per, kt_hi = (kt_lo + per < n_kt) ? kt_lo + per : n_kt;
+  const int* pages = a.page_map + size_t(grp) * a.max_pages;
+
+  // stage Q (rows beyond the tile are zero), the mixing matrix and the head bias
+  for (int idx = tid; idx < kWmmaRows * (H * d / 8); idx += kWmmaThreads) {
+    const int row = idx / (H * d / 8), c8 = idx % (H * d / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < nrows) v = *reinterpret_cast<const uint4*>(a.q + size_t(r0 + row) * H * d + c8 * 8);
+    *reinterpret_cast<uint4*>(sQ + row * QP + c8 * 8) = v;
+  }
+  for (int e = tid; e < H * H; e += kWmmaThreads) sTalk[e] = a.talk ? a.talk[e] : ((e / H == e % H) ? 1.0f : 0.0f);
+  for (int e = tid; e < H; e += kWmmaThreads) sPb[e] = a.head_bias ? a.head_bias[e] : 0.0f;
+
+  float acc[HPW][DVT][4];
+#pragma unroll
+  for (int u = 0; u < HPW; ++u)
+#pragma unroll
+    for (int nt = 0; nt < DVT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[u][nt][e] = 0.0f;
+
+  const float inv_cap = a.softcap > 0.0f ? 1.0f / a.softcap : 0.0f;
+  for (int kt = kt_lo; kt < kt_hi; ++kt) {
+    const int j0 = klo + kt * BN;
+    if (tid < BN) {
+      const int j = j0 + tid;
+      sRow[tid] = j <= khi ? pages[j / a.tokens_per_page] * a.tokens_per_page + j % a.tokens_per_page : -1;
+    }
+    __syncthreads();  // the previous tile's PV phase is over, the rows of this one are known
+    for (int idx = tid; idx < G * BN * (d / 8); idx += kWmmaThreads) {
+      const int c8 = idx % (d / 8), key = (idx / (d / 8)) % BN, c = idx / ((d / 8) * BN);
+      const int row = sRow[key];
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row >= 0) v = *reinterpret_cast<const uint4*>(a.k_pages + (size_t(c) * a.num_pages * a.tokens_per_page + row) * d + c8 * 8);
+      *reinterpret_cast<uint4*>(sK + (c * BN + key) * KP + c8 * 8) = v;
+    }
+    for (int idx = tid; idx < G * BN * (dv / 8); idx += kWmmaThreads) {
+      const int c8 = idx % (dv / 8), key = (idx / (dv / 8)) % BN, c = idx / ((dv / 8) * BN);
+      const int row = sRow[key];
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row >= 0) v = *reinterpret_cast<const uint4*>(a.v_pages + (size_t(c) * a.num_pages * a.tokens_per_page + row) * dv + c8 * 8);
+      *reinterpret_cast<uint4*>(sV + (c * BN + key) * VP + c8 * 8) = v;
+    }
+    __syncthreads();
+    // ---- S phase: this warp's 8 keys, every head ----
+    if (warp * 8 < BN) {
+      float w[HMAX][4];
+#pragma unroll
+      for (int g = 0; g < HMAX; ++g) {
+        if (g < H) {
+          float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          const bf16* qb = sQ + g4 * QP + g * d + 2 * t4;
+          const bf16* kb = sK + ((g / rep) * BN + warp * 8 + g4) * KP + 2 * t4;
+          for (int ks = 0; ks < d; ks += 16) {
+            uint32_t af[4];
+            af[0] = *reinterpret_cast<const uint32_t*>(qb + ks);
+            af[1] = *reinterpret_cast<const uint32_t*>(qb + ks + 8 * QP);
+            af[2] = *reinterpret_cast<const uint32_t*>(qb + ks + 8);
+            af[3] = *reinterpret_cast<const uint32_t*>(qb + ks + 8 * QP + 8);
+            mma_bf16_16816(s, af, *reinterpret_cast<const uint32_t*>(kb + ks), *reinterpret_cast<const uint32_t*>(kb + ks + 8));
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int ir = g4 + (e >> 1) * 8, i = p0 + ir, j = j0 + warp * 8 + 2 * t4 + (e & 1);
+            float wv = 0.0f;
+            if (ir < nrows && j <= i && i - j < a.window) {
+              float sc = s[e] * a.scale;
+              if (a.softcap > 0.0f) sc = a.softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * sc * inv_cap) + 1.0f));  // cap * tanh(sc / cap)
+              sc += __ldg(a.dist_bias + size_t(i - j) * H + g) + sPb[g];
+              wv = __fdividef(1.0f, 1.0f + __expf(-sc));
+            }
+            w[g][e] = wv;
+          }
+        }
+      }
+      // mix the heads' weights; P_h as bf16
+#pragma unroll 1
+      for (int h = 0; h < H; ++h) {
+        float m[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float* tr = sTalk + h * H;
+#pragma unroll
+        for (int g = 0; g < HMAX; ++g) {
+          if (g < H) {
+            const float tv = tr[g];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) m[e] = fmaf(tv, w[g][e], m[e]);
+          }
+        }
+        bf16* pb = sP + (h * kWmmaRows + g4) * PP + warp * 8 + 2 * t4;
+        *reinterpret_cast<uint32_t*>(pb) = pack_bf16x2(m[0], m[1]);
+        *reinterpret_cast<uint32_t*>(pb + 8 * PP) = pack_bf16x2(m[2], m[3]);
+      }
+    }
+    __syncthreads();
+    // ---- PV phase: this warp's heads ----
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+      const int h = warp * HPW + u;
+      if (h < H) {
+        const bf16* pb = sP + (h * kWmmaRows + g4) * PP + 2 * t4;
+        const bf16* vb = sV + (h / rep) * BN * VP;
+        for (int k2 = 0; k2 < BN; k2 += 16) {
+          uint32_t af[4];
+          af[0] = *reinterpret_cast<const uint32_t*>(pb + k2);
+          af[1] = *reinterpret_cast<const uint32_t*>(pb + k2 + 8 * PP);
+          af[2] = *reinterpret_cast<const uint32_t*>(pb + k2 + 8);
+          af[3] = *reinterpret_cast<const uint32_t*>(pb + k2 + 8 * PP + 8);
+#pragma unroll
+          for (int nt = 0; nt < DVT; ++nt) {
+            if (nt * 8 < dv) {
+              uint32_t b0, b1;
+              const uint32_t addr = smem_u32(vb + (k2 + (lane & 15)) * VP + nt * 8);  // lanes 0-15: the 16 key rows of this k step
+              asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+              mma_bf16_16816(acc[u][nt], af, b0, b1);
+            }
+          }
+        }
+      }
+    }
+  }
+  // this split's partial sums (zeros if it had no keys)
+  const size_t out_row = size_t(H) * dv;
+  float* part = x.partial + size_t(split) * a.rows * out_row;
+#pragma unroll
+  for (int u = 0; u < HPW; ++u) {
+    const int h = warp * HPW + u;
+    if (h < H) {
+#pragma unroll
+      for (int nt = 0; nt < DVT; ++nt) {
+        if (nt * 8 < dv) {
+          const int col = h * dv + nt * 8 + 2 * t4;
+          if (g4 < nrows) *reinterpret_cast<float2*>(part + size_t(r0 + g4) * out_row + col) = make_float2(acc[u][nt][0], acc[u][nt][1]);
+          if (g4 + 8 < nrows) *reinterpret_cast<float2*>(part + size_t(r0 + g4 + 8) * out_row + col) = make_float2(acc[u][nt][2], acc[u][nt][3]);
+        }
+      }
+    }
+  }
+}
+
+// out[r, o] = bf16(sum over the splits, in order)
+__global__ void window_partial_sum_kernel(const float* partial, bf16* out, int splits, long long per_split) {
+  griddep_wait();
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 2; i < per_split; i += (long long)gridDim.x * blockDim.x * 2) {
+    float2 s = *reinterpret_cast<const float2*>(partial + i);
+    for (int p = 1; p < splits; ++p) {
+      const float2 v = *reinterpret_cast<const float2*>(partial + p * per_split + i);
+      s.x += v.x;
+      s.y += v.y;
+    }
+    *reinterpret_cast<uint32_t*>(out + i) = pack_bf16x2(s.x, s.y);
+  }
+}
+
+struct WindowMmaPlan {
+  bool ok = false;
+  int hpw = 0, dvt = 0, bn = 0;
+  size_t smem = 0;
+};
+
+// Which instantiation serves this head geometry, if any: bf16, dim and vdim multiples of 16 (fragments and 16-byte rows), at most
+// 16 heads, HPW * DVT <= 32 accumulator tiles per thread, shared memory within the SM's.
+inline WindowMmaPlan window_mma_plan(int heads, int kv_heads, int dim, int vdim) {
+  WindowMmaPlan p;
+  if (dim % 16 != 0 || vdim % 16 != 0 || heads > 16 || heads % kv_heads != 0) return p;
+  p.hpw = heads <= 8 ? 1 : 2;
+  const int need = (vdim + 7) / 8;
+  p.dvt = need <= 8 ? 8 : (need <= 16 ? 16 : 32);
+  if (need > 32 || p.hpw * p.dvt > 32) return p;
+  for (int bn = 64; bn >= 32; bn /= 2) {
+    const size_t s = window_mma_smem_bytes(heads, kv_heads, dim, vdim, bn);
+    if (s <= 220 * 1024) {
+      p.bn = bn;
+      p.smem = s;
+      p.ok = true;
+      return p;
+    }
+  }
+  return p;
+}
 
 }  // namespace mtx

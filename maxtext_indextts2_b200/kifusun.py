@@ -141,7 +141,7 @@ def random_tensors(config, seed: int = 0, device: Any = "cpu", bias_rows: int = 
   bf = torch.bfloat16
 
   def rn(*shape, std=1.0, mean=0.0):
-    return (torch.randn(*shape, generator=g, device=device) * std + mean).to(bf)
+    return (torch.randn(tuple(shape), generator=g, device=device) * std + mean).to(bf)
 
   t = {"embed": rn(V, E, std=1.0 / math.sqrt(E)), "final.norm": rn(std=0.05, mean=1.0), "head": rn(V, E, std=1.0 / math.sqrt(E))}
   for i, l in enumerate(config.layer_specs):

@@ -28,6 +28,7 @@ from . import params as params_lib
 from .maxengine import ExistingPrefix, MaxEngine, ResultTokens  # noqa: F401  (same result types)
 
 _MIXERS = {"window_sigmoid": _lib.MIXER_WINDOW_SIGMOID}
+QUERY_TILE_ROWS = 16  # rows of one query tile of the tensor-core mixer (csrc/window_attention_mma.cuh)
 
 
 def design_module(config):
@@ -107,9 +108,10 @@ class LayeredEngine(MaxEngine):
     MP = self.page_manager.max_pages_per_group
     self._page_map_dev = torch.zeros(B, MP, dtype=i32, device=dev)
     self._uploaded_map = None
-    # one pinned staging buffer per step: [token | group | pos | want] rows
-    self._desc_host = torch.zeros(4 * self._max_rows, dtype=i32).pin_memory()
-    self._desc_dev = torch.zeros(4 * self._max_rows, dtype=i32, device=dev)
+    # one pinned staging buffer per step: [token | group | pos | want | query tiles] rows
+    self._desc_host = torch.zeros(5 * self._max_rows + 8, dtype=i32).pin_memory()
+    self._desc_dev = torch.zeros(5 * self._max_rows + 8, dtype=i32, device=dev)
+    self._decode_tiles = torch.arange(B + 1, dtype=i32, device=dev)  # a decode step: every row is its own query tile
     self._sample_scratch = torch.zeros(5 * max(B, 1), dtype=torch.float32, device=dev)
     self._first_token = torch.zeros(1, dtype=i32, device=dev)
     self._first_log_prob = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -228,9 +230,11 @@ class LayeredEngine(MaxEngine):
 
   # -- the ragged step ----------------------------------------------------------------------------
 
-  def _run(self, rows: int, token_ptr: int, group_ptr: int, pos_ptr: int, n_want: int, want_ptr: int, logits: Optional[torch.Tensor]) -> None:
+  def _run(self, rows: int, token_ptr: int, group_ptr: int, pos_ptr: int, n_want: int, want_ptr: int, logits: Optional[torch.Tensor],
+           n_tiles: int = 0, tiles_ptr: Optional[int] = None) -> None:
     b = _lib.RaggedBatch(rows=rows, token=token_ptr, group=group_ptr, pos=pos_ptr, page_map=self._page_map_dev.data_ptr(), n_want=n_want,
-                         want_rows=want_ptr if n_want else None, logits=logits.data_ptr() if n_want else None)
+                         want_rows=want_ptr if n_want else None, logits=logits.data_ptr() if n_want else None,
+                         n_tiles=n_tiles, tile_row0=tiles_ptr if n_tiles else None)
     _lib.check(self.lib.mtx_layered_step(self._handle, ctypes.byref(b), self._stream()))
 
   def step(self, entries: Sequence[Tuple[int, Sequence[int], Sequence[int]]]) -> torch.Tensor:
@@ -239,7 +243,7 @@ class LayeredEngine(MaxEngine):
     logits [n, vocab] (fp32, on the device) in the order of the entries.  Steps longer than max_step_rows run in slices."""
     self._require_params(None)
     B, V = self.max_concurrent_decodes, int(self.config.vocab_size)
-    tok, grp, pos, want = [], [], [], []
+    tok, grp, pos, want, runs = [], [], [], [], []
     ps = self.page_state
     seen = set()
     for slot, tokens, wanted in entries:
@@ -256,6 +260,7 @@ class LayeredEngine(MaxEngine):
         raise ValueError(f"slot {slot}: the page pool cannot hold {start + n} tokens")
       ps = new
       base = len(tok)
+      runs.append((base, base + n))
       tok.extend(int(t) for t in tokens)
       grp.extend([slot] * n)
       pos.extend(range(start, start + n))
@@ -281,12 +286,19 @@ class LayeredEngine(MaxEngine):
       host[2 * R : 2 * R + n] = torch.tensor(pos[lo:hi], dtype=torch.int32)
       if w:
         host[3 * R : 3 * R + len(w)] = torch.tensor(w, dtype=torch.int32)
+      # query tiles: every run of consecutive positions (an entry, cut at the slice) in pieces of at most 16 rows
+      tiles = []
+      for a, b in runs:
+        a, b = max(a, lo), min(b, hi)
+        tiles.extend(range(a - lo, b - lo, QUERY_TILE_ROWS))
+      tiles.append(n)
+      host[4 * R : 4 * R + len(tiles)] = torch.tensor(tiles, dtype=torch.int32)
       if lo:
         torch.cuda.current_stream(self.device).synchronize()  # the previous slice has read the staging buffer
       self._desc_dev.copy_(host, non_blocking=True)
       p = self._desc_dev.data_ptr()
       dst = out[done_want : done_want + len(w)]
-      self._run(n, p, p + 4 * R, p + 8 * R, len(w), p + 12 * R, dst)
+      self._run(n, p, p + 4 * R, p + 8 * R, len(w), p + 12 * R, dst, len(tiles) - 1, p + 16 * R)
       done_want += len(w)
     torch.cuda.current_stream(self.device).synchronize()  # the pinned staging buffer is free again when step returns
     return out
@@ -366,7 +378,8 @@ class LayeredEngine(MaxEngine):
       raise ValueError(f"the page pool is exhausted: slots {np.flatnonzero(grew).tolist()} cannot grow")
     self.page_state = ps
     self._upload_page_map()
-    self._run(B, self._tokens.data_ptr(), self._slot_ids.data_ptr(), self._next_pos.data_ptr(), B, self._slot_ids.data_ptr(), self._logits)
+    self._run(B, self._tokens.data_ptr(), self._slot_ids.data_ptr(), self._next_pos.data_ptr(), B, self._slot_ids.data_ptr(), self._logits,
+              B, self._decode_tiles.data_ptr())
     self._sample(self._logits.view(B, -1), B, self._tokens, self._log_prob, 0)
     # bookkeeping of maxengine.py:913-928 for the occupied slots (empty ones stay at position 0 on page 0)
     self._next_pos.add_(self._active)

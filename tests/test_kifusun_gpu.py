@@ -335,3 +335,66 @@ def test_greedy_generation_through_the_offline_engine():
       assert float(top2[0] - top2[1]) > 1e-4, "near-tie in the test's own model; change the seed"
       seq.append(int(logits.argmax()))
     assert out.token_ids.tolist() == seq[len(prompt):]
+
+
+# ---- the tensor-core mixer (bf16, head sizes in multiples of 16) ---------------------------------------------------------------------
+
+def _rms_err(got, want):
+  rms = lambda a: float(a.pow(2).mean().sqrt())
+  return rms(got - want) / rms(want)
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,page", [
+    (4, 2, 32, 16, 5, 4), (8, 8, 16, 48, 33, 16), (16, 4, 64, 64, 100, 8), (12, 3, 48, 32, 20, 4), (2, 1, 128, 128, 70, 16),
+    (1, 1, 16, 256, 9, 4), (4, 2, 96, 64, 40, 8)])
+def test_tensor_core_mixer_shapes_and_schedules(heads, kv_heads, dim, vdim, window, page):
+  cfg = model([layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=window, ff=0, bias_max=float(window + 3)),
+               layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=max(2, window // 2), ff=48)], width=64, vocab=90)
+  t = ref.random_model(cfg, seed=23)
+  oracle = ref.KifusunRef(cfg, t)
+  toks = {k: tokens_for(cfg, n, seed=n) for k, n in (("a", 131), ("b", 37), ("c", 18))}
+  want = {k: oracle.forward(v) for k, v in toks.items()}
+  engine, _ = make_engine(cfg, t, dtype="bfloat16", tokens_per_page=page, num_pages=200 // page * 2, max_len=200)
+  for k in toks:  # whole prompts: query tiles of 16 rows, the last one ragged
+    assert _rms_err(whole(engine, toks[k]), want[k]) < 2e-2, k
+  # a mixed batch: portions of a and b beside single tokens of c, then everything decoded token by token
+  got = {k: [] for k in toks}
+  at = {k: 0 for k in toks}
+  slot = {"a": 0, "b": 1, "c": 2}
+  for sizes in ({"a": 50, "b": 3, "c": 1}, {"a": 17, "b": 20, "c": 1}, {"a": 33, "c": 1}):
+    entries = [(slot[k], toks[k][at[k] : at[k] + n], list(range(n))) for k, n in sizes.items()]
+    out = engine.step(entries).cpu().double()
+    for k, n in sizes.items():
+      got[k].append(out[:n])
+      out = out[n:]
+      at[k] += n
+  while any(at[k] < len(toks[k]) for k in toks):
+    live = [k for k in toks if at[k] < len(toks[k])]
+    out = engine.step([(slot[k], [toks[k][at[k]]], [0]) for k in live]).cpu().double()
+    for i, k in enumerate(live):
+      got[k].append(out[i : i + 1])
+      at[k] += 1
+  for k in toks:
+    assert _rms_err(torch.cat(got[k]), want[k]) < 2e-2, k
+
+
+@pytest.mark.parametrize("window,page", [(16, 8), (17, 4), (33, 16), (64, 16), (65, 64)])
+def test_tensor_core_mixer_window_edges(window, page):
+  rows = 24 if window > 40 else 12  # (more rows in the distance table: a narrower last bucket, fewer open keys)
+  cfg = model([layer(heads=4, kv_heads=2, dim=32, vdim=16, window=window, bias_max=float(window - 1), ff=0),
+               layer(heads=4, kv_heads=2, dim=32, vdim=16, window=window, bias_max=float(window - 1))])
+  t = _spiked(cfg, rows)
+  toks = tokens_for(cfg, 2 * window + 21)
+  want = ref.KifusunRef(cfg, t).forward(toks)
+  for other in (window - 1, window + 1):  # an off-by-one window would be far outside the tolerance below
+    c2 = copy.deepcopy(cfg)
+    for l in c2["layers"]:
+      l["mixer"]["mask"]["size"] = other
+    assert _rms_err(ref.KifusunRef(c2, t).forward(toks), want) > 8e-2
+  engine, _ = make_engine(cfg, t, dtype="bfloat16", tokens_per_page=page, num_pages=600 // page, max_len=256)
+  assert _rms_err(whole(engine, toks), want) < 2e-2
+  for cut in (window - 1, window, window + 1, 16, 17):
+    head = engine.step([(1, toks[:cut], list(range(cut)))]).cpu().double()
+    tail = [engine.step([(1, [tok], [0])]).cpu().double() for tok in toks[cut:]]
+    engine.release_pages(1)
+    assert _rms_err(torch.cat([head] + tail), want) < 2e-2, cut
