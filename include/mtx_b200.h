@@ -429,6 +429,9 @@ size_t mtx_layered_workspace_bytes(const mtx_layered* e);
 int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes);
 /* All layers for the rows of `b` (appending their keys / values to the pages), then the logits of the wanted rows. */
 int mtx_layered_step(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream stream);
+/* The same step replayed from a CUDA graph that is captured the first time a descriptor (all fields of `b`, pointers included) is
+ * seen: for a decode loop, whose descriptor never changes while the arrays behind it do. */
+int mtx_layered_step_graph(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream stream);
 
 /* inference_utils.sampling (:66-111) on a logits matrix, without an engine: greedy / weighted / nucleus / top-k as
  * mtx_sample_logits does it.  rng_state: 4 x uint32 device words ([0] = draw counter, [1..2] = seed); scratch: 5 * rows floats. */

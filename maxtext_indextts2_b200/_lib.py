@@ -316,6 +316,8 @@ def _declare(lib) -> None:
   lib.mtx_layered_bind.argtypes = [vp, vp, sz]
   lib.mtx_layered_step.restype = i32
   lib.mtx_layered_step.argtypes = [vp, c.POINTER(RaggedBatch), vp]
+  lib.mtx_layered_step_graph.restype = i32
+  lib.mtx_layered_step_graph.argtypes = [vp, c.POINTER(RaggedBatch), vp]
   lib.mtx_sample_rows.restype = i32
   lib.mtx_sample_rows.argtypes = [vp, i32, c.c_longlong, i32, i32, i32, f32, f32, vp, i32, vp, vp, vp, vp]
   lib.mtx_engine_rebind_state.restype = i32

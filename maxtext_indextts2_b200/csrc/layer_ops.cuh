@@ -47,7 +47,9 @@ __global__ void embed_rows_kernel(const int* token, const T* embedding, int voca
 
 template <typename T>
 struct QkvPostArgs {
-  const float* qkv;   // [rows, H*d + G*d + G*dv]: the projection with its bias
+  const float* qkv;   // [rows, H*d + G*d + G*dv]: the projection with its bias, or null:
+  const bf16* qkv_bf16;  // the projection as the tcgen05 GEMM left it (bf16, no bias) and
+  const float* bias;     // its bias [H*d + G*d + G*dv] (or null)
   const float* q_norm;  // [d] or null (no normalisation)
   const float* k_norm;  // [d] or null
   T* q_out;           // [rows, H*d]
@@ -70,24 +72,29 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(const QkvPostArgs<T> a) {
   const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
   const int H = a.heads, G = a.kv_heads, d = a.dim, dv = a.vdim;
   const int n_all = H * d + G * d + G * dv;
-  const float* row = a.qkv + size_t(r) * n_all;
+  const float* rowf = a.qkv ? a.qkv + size_t(r) * n_all : nullptr;
+  const bf16* rowb = a.qkv ? nullptr : a.qkv_bf16 + size_t(r) * n_all;
+  auto val = [&](int c) { return rowf ? rowf[c] : __bfloat162float(rowb[c]) + (a.bias ? a.bias[c] : 0.0f); };
   const int p = a.pos[r], grp = a.group[r];
   const size_t slot = size_t(a.page_map[size_t(grp) * a.max_pages + p / a.tokens_per_page]) * a.tokens_per_page + p % a.tokens_per_page;
   for (int u = warp; u < H + G; u += nw) {  // unit u: query head u, or key head u - H
     const bool is_q = u < H;
-    const float* src = row + (is_q ? u * d : H * d + (u - H) * d);
+    const int src = is_q ? u * d : H * d + (u - H) * d;
     const float* w = is_q ? a.q_norm : a.k_norm;
     float ss = 0.0f;
-    for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
+    for (int c = lane; c < d; c += 32) {
+      const float v = val(src + c);
+      ss = fmaf(v, v, ss);
+    }
     ss = warp_sum(ss);
     const float inv = w ? 1.0f / sqrtf(ss / float(d) + a.eps) : 1.0f;
     T* dst = is_q ? a.q_out + size_t(r) * H * d + u * d
                   : a.k_pages + (size_t(u - H) * a.num_pages * a.tokens_per_page + slot) * d;
-    for (int c = lane; c < d; c += 32) dst[c] = to_act<T>(w ? src[c] * inv * w[c] : src[c]);
+    for (int c = lane; c < d; c += 32) dst[c] = to_act<T>(w ? val(src + c) * inv * w[c] : val(src + c));
   }
-  const float* vsrc = row + H * d + G * d;
+  const int vsrc = H * d + G * d;
   for (int e = tid; e < G * dv; e += blockDim.x) {
-    float v = vsrc[e];
+    float v = val(vsrc + e);
     if (a.value_mix == 1) a.v_shared[size_t(r) * G * dv + e] = v;
     else if (a.value_mix == 2) v = (1.0f - a.value_lambda) * v + a.value_lambda * a.v_shared[size_t(r) * G * dv + e];
     const int kv = e / dv, c = e % dv;
@@ -95,18 +102,24 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(const QkvPostArgs<T> a) {
   }
 }
 
+// (y as fp32, or -- y null -- as the bf16 matrix y_bf16 a tcgen05 GEMM left)
 template <typename T>
-__global__ void __launch_bounds__(256) norm_residual_kernel(const float* y, float gain, float eps, float* x, T* xa, int width) {
+__global__ void __launch_bounds__(256) norm_residual_kernel(const float* y, const bf16* y_bf16, float gain, float eps, float* x, T* xa, int width) {
   __shared__ float red[8];
   griddep_wait();
   const int r = blockIdx.x;
-  const float* yr = y + size_t(r) * width;
+  const float* yf = y ? y + size_t(r) * width : nullptr;
+  const bf16* yb = y ? nullptr : y_bf16 + size_t(r) * width;
+  auto val = [&](int c) { return yf ? yf[c] : __bfloat162float(yb[c]); };
   float ss = 0.0f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(yr[c], yr[c], ss);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = val(c);
+    ss = fmaf(v, v, ss);
+  }
   ss = block_sum(ss, red);
   const float f = gain / sqrtf(ss / float(width) + eps);
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    const float v = x[size_t(r) * width + c] + yr[c] * f;
+    const float v = x[size_t(r) * width + c] + val(c) * f;
     x[size_t(r) * width + c] = v;
     xa[size_t(r) * width + c] = to_act<T>(v);
   }

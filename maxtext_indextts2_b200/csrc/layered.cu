@@ -26,6 +26,13 @@ struct mtx_layered {
   // workspace carve-up
   float *x = nullptr, *y = nullptr, *qkv = nullptr, *v_shared = nullptr;
   void *xa = nullptr, *q = nullptr, *attn = nullptr, *act = nullptr, *wanted = nullptr, *obf = nullptr;
+  // mtx_layered_step_graph: one instantiated graph per distinct batch descriptor (a decode loop passes the same one every step)
+  struct GraphEntry {
+    mtx_ragged_batch key;
+    cudaGraphExec_t exec;
+  };
+  std::vector<GraphEntry> graphs;
+  cudaStream_t cap_stream = nullptr;
   float* attn_part = nullptr;  // fp32 partial outputs of the attention's key splits: room for 2 * max_rows rows
   size_t attn_part_rows = 0;
 };
@@ -107,9 +114,8 @@ int run_linear(mtx_layered* e, const void* a, const void* w, const float* bias, 
   else return launch(linear_mma_kernel<EPI>, grid, dim3(kLinThreads), 0, st, p);
 }
 
-// the same product on the tcgen05 GEMM (bf16 result in e->obf, 256-row blocks), then the epilogue as a row kernel
-template <int EPI>
-int run_linear_umma(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st) {
+// the same product on the tcgen05 GEMM: the bf16 result stays in e->obf (256-row blocks)
+int run_umma_raw(mtx_layered* e, const void* a, const void* w, int rows, int n, int k, cudaStream_t st) {
   bf16* tmp = static_cast<bf16*>(e->obf);
   for (int r0 = 0; r0 < rows; r0 += 256) {
     const int nr = rows - r0 < 256 ? rows - r0 : 256;
@@ -119,16 +125,26 @@ int run_linear_umma(mtx_layered* e, const void* a, const void* w, const float* b
     ea.ld_out = n;
     MTX_TRY(single_gemm<EPI_STORE_BF16>(static_cast<const bf16*>(a) + size_t(r0) * k, w, nr, n, k, ea, st));
   }
+  return MTX_OK;
+}
+
+// ... then the epilogue as a row kernel
+template <int EPI>
+int run_linear_umma(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st) {
+  MTX_TRY(run_umma_raw(e, a, w, rows, n, k, st));
+  const bf16* tmp = static_cast<const bf16*>(e->obf);
   const long long total = (long long)rows * (EPI == LIN_GATED ? n / 2 : n);
   const int blocks = int((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  if (EPI == LIN_GATED) return launch(gate_up_bf16_kernel, dim3(blocks), dim3(256), 0, st, (const bf16*)tmp, static_cast<bf16*>(act), n / 2, total);
-  return launch(bf16_rows_to_f32_kernel, dim3(blocks), dim3(256), 0, st, (const bf16*)tmp, bias, out, n, total);
+  if (EPI == LIN_GATED) return launch(gate_up_bf16_kernel, dim3(blocks), dim3(256), 0, st, tmp, static_cast<bf16*>(act), n / 2, total);
+  return launch(bf16_rows_to_f32_kernel, dim3(blocks), dim3(256), 0, st, tmp, bias, out, n, total);
 }
+
+bool takes_umma(const mtx_layered* e, int rows, int n, int k) { return fits_umma(e, n, k) && rows >= 16; }
 
 template <typename T, int EPI>
 int linear(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st) {
   if constexpr (sizeof(T) == 2) {
-    if (fits_umma(e, n, k) && rows >= 16) return run_linear_umma<EPI>(e, a, w, bias, out, act, rows, n, k, st);
+    if (takes_umma(e, rows, n, k)) return run_linear_umma<EPI>(e, a, w, bias, out, act, rows, n, k, st);
   }
   return run_linear<T, EPI>(e, a, w, bias, out, act, rows, n, k, st);
 }
@@ -137,6 +153,21 @@ int pick_key_tile(const mtx_layer_desc& l) {
   int kt = 32;
   while (kt > 4 && window_attn_smem_bytes(l.heads, l.kv_heads, l.dim, l.vdim, kt) > 200 * 1024) kt /= 2;
   return kt;
+}
+
+// x += gain * unit(a . w^T), and the copy of x in the matmul dtype
+template <typename T>
+int project_norm_residual(mtx_layered* e, const void* a, const void* w, int rows, int n, int k, float gain, cudaStream_t st) {
+  const float* y = e->y;
+  const bf16* yb = nullptr;
+  if (sizeof(T) == 2 && takes_umma(e, rows, n, k)) {
+    MTX_TRY(run_umma_raw(e, a, w, rows, n, k, st));
+    y = nullptr;
+    yb = static_cast<const bf16*>(e->obf);
+  } else {
+    MTX_TRY((linear<T, LIN_PLAIN>(e, a, w, nullptr, e->y, nullptr, rows, n, k, st)));
+  }
+  return launch(norm_residual_kernel<T>, dim3(rows), dim3(256), 0, st, y, yb, gain, e->cfg.eps, e->x, static_cast<T*>(e->xa), e->cfg.width);
 }
 
 bool use_window_mma() {
@@ -190,11 +221,17 @@ int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
     const mtx_layer_desc& l = e->layers[li];
     const int H = l.heads, G = l.kv_heads, nq = H * l.dim, nqkv = nq + G * l.dim + G * l.vdim, no = H * l.vdim;
     // q, k, v = W x + b
-    if (l.bqkv) MTX_TRY((linear<T, LIN_BIAS>(e, xa, l.wqkv, l.bqkv, e->qkv, nullptr, rows, nqkv, E, st)));
-    else MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.wqkv, nullptr, e->qkv, nullptr, rows, nqkv, E, st)));
     QkvPostArgs<T> qa;
     memset(&qa, 0, sizeof(qa));
-    qa.qkv = e->qkv;
+    if (sizeof(T) == 2 && takes_umma(e, rows, nqkv, E)) {  // the tcgen05 GEMM's bf16 result; the bias is added where it is read
+      MTX_TRY(run_umma_raw(e, xa, l.wqkv, rows, nqkv, E, st));
+      qa.qkv_bf16 = static_cast<const bf16*>(e->obf);
+      qa.bias = l.bqkv;
+    } else {
+      if (l.bqkv) MTX_TRY((linear<T, LIN_BIAS>(e, xa, l.wqkv, l.bqkv, e->qkv, nullptr, rows, nqkv, E, st)));
+      else MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.wqkv, nullptr, e->qkv, nullptr, rows, nqkv, E, st)));
+      qa.qkv = e->qkv;
+    }
     qa.q_norm = l.q_norm;
     qa.k_norm = l.k_norm;
     qa.q_out = static_cast<T*>(e->q);
@@ -259,13 +296,11 @@ int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
       MTX_TRY(launch(window_attention_rows_kernel<T>, dim3(rows), dim3(kWinThreads), smem, st, wa));
     }
     // x += gain1 * unit(Wo attn)
-    MTX_TRY((linear<T, LIN_PLAIN>(e, e->attn, l.wo, nullptr, e->y, nullptr, rows, E, no, st)));
-    MTX_TRY(launch(norm_residual_kernel<T>, dim3(rows), dim3(256), 0, st, (const float*)e->y, l.gain1, c.eps, e->x, xa, E));
+    MTX_TRY(project_norm_residual<T>(e, e->attn, l.wo, rows, E, no, l.gain1, st));
     if (l.ff > 0) {
       // x += gain2 * unit(Wdown (gelu(Wgate x) * Wup x))
       MTX_TRY((linear<T, LIN_GATED>(e, xa, l.w_gate_up, nullptr, nullptr, e->act, rows, 2 * l.ff, E, st)));
-      MTX_TRY((linear<T, LIN_PLAIN>(e, e->act, l.w_down, nullptr, e->y, nullptr, rows, E, l.ff, st)));
-      MTX_TRY(launch(norm_residual_kernel<T>, dim3(rows), dim3(256), 0, st, (const float*)e->y, l.gain2, c.eps, e->x, xa, E));
+      MTX_TRY(project_norm_residual<T>(e, e->act, l.w_down, rows, E, l.ff, l.gain2, st));
     }
   }
   if (b.n_want > 0) {
@@ -331,6 +366,9 @@ int mtx_layered_create(const mtx_layered_config* cfg, const mtx_layer_desc* laye
 }
 
 int mtx_layered_destroy(mtx_layered* e) {
+  if (e == nullptr) return MTX_OK;
+  for (auto& g : e->graphs) cudaGraphExecDestroy(g.exec);
+  if (e->cap_stream) cudaStreamDestroy(e->cap_stream);
   delete e;
   return MTX_OK;
 }
@@ -367,6 +405,37 @@ int mtx_layered_step(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream strea
   if (b->n_tiles < 0 || b->n_tiles > b->rows) return fail(MTX_ERR_ARG, "n_tiles = %d for %d rows", b->n_tiles, b->rows);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return e->cfg.float32 ? step_typed<float>(e, *b, st) : step_typed<bf16>(e, *b, st);
+}
+
+int mtx_layered_step_graph(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream stream) {
+  if (!e || !e->bound || !b) return fail(MTX_ERR_ARG, "engine is not bound / null argument");
+  for (auto& g : e->graphs) {
+    if (memcmp(&g.key, b, sizeof(*b)) == 0) {
+      MTX_CUDA(cudaGraphLaunch(g.exec, static_cast<cudaStream_t>(stream)));
+      return MTX_OK;
+    }
+  }
+  if (e->graphs.size() >= 64) return mtx_layered_step(e, b, stream);  // (a caller that never repeats a descriptor)
+  if (!e->cap_stream) MTX_CUDA(cudaStreamCreateWithFlags(&e->cap_stream, cudaStreamNonBlocking));
+  cudaGraph_t graph = nullptr;
+  MTX_CUDA(cudaStreamBeginCapture(e->cap_stream, cudaStreamCaptureModeThreadLocal));
+  const int rc = mtx_layered_step(e, b, e->cap_stream);
+  const cudaError_t end = cudaStreamEndCapture(e->cap_stream, &graph);
+  if (rc != MTX_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (end != cudaSuccess) return fail(MTX_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(end));
+  cudaGraphExec_t exec = nullptr;
+  const cudaError_t inst = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (inst != cudaSuccess) return fail(MTX_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(inst));
+  mtx_layered::GraphEntry ge;
+  memcpy(&ge.key, b, sizeof(*b));
+  ge.exec = exec;
+  e->graphs.push_back(ge);
+  MTX_CUDA(cudaGraphLaunch(exec, static_cast<cudaStream_t>(stream)));
+  return MTX_OK;
 }
 
 }  // extern "C"

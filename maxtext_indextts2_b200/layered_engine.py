@@ -231,11 +231,12 @@ class LayeredEngine(MaxEngine):
   # -- the ragged step ----------------------------------------------------------------------------
 
   def _run(self, rows: int, token_ptr: int, group_ptr: int, pos_ptr: int, n_want: int, want_ptr: int, logits: Optional[torch.Tensor],
-           n_tiles: int = 0, tiles_ptr: Optional[int] = None) -> None:
+           n_tiles: int = 0, tiles_ptr: Optional[int] = None, graph: bool = False) -> None:
     b = _lib.RaggedBatch(rows=rows, token=token_ptr, group=group_ptr, pos=pos_ptr, page_map=self._page_map_dev.data_ptr(), n_want=n_want,
                          want_rows=want_ptr if n_want else None, logits=logits.data_ptr() if n_want else None,
                          n_tiles=n_tiles, tile_row0=tiles_ptr if n_tiles else None)
-    _lib.check(self.lib.mtx_layered_step(self._handle, ctypes.byref(b), self._stream()))
+    fn = self.lib.mtx_layered_step_graph if graph else self.lib.mtx_layered_step
+    _lib.check(fn(self._handle, ctypes.byref(b), self._stream()))
 
   def step(self, entries: Sequence[Tuple[int, Sequence[int], Sequence[int]]]) -> torch.Tensor:
     """One mixed batch.  `entries`: (slot, the sequence's next tokens, indices among them whose logits are wanted).  Every
@@ -379,7 +380,7 @@ class LayeredEngine(MaxEngine):
     self.page_state = ps
     self._upload_page_map()
     self._run(B, self._tokens.data_ptr(), self._slot_ids.data_ptr(), self._next_pos.data_ptr(), B, self._slot_ids.data_ptr(), self._logits,
-              B, self._decode_tiles.data_ptr())
+              B, self._decode_tiles.data_ptr(), graph=self.use_cuda_graph)
     self._sample(self._logits.view(B, -1), B, self._tokens, self._log_prob, 0)
     # bookkeeping of maxengine.py:913-928 for the occupied slots (empty ones stay at position 0 on page 0)
     self._next_pos.add_(self._active)
