@@ -31,13 +31,27 @@ struct WindowMmaExtra {
 inline size_t window_mma_smem_bytes(int heads, int kv_heads, int dim, int vdim, int bn) {
   return size_t(2) * (size_t(kWmmaRows) * (heads * dim + 8) + size_t(kv_heads) * bn * (dim + 8) + size_t(kv_heads) * bn * (vdim + 8) +
                       size_t(heads) * kWmmaRows * (bn + 8)) +
-         sizeof(float) * (size_t(heads) * heads + heads) + sizeof(int) * 64;
+         sizeof(float) * (size_t(heads) * 16 + heads + size_t(bn + kWmmaRows) * heads) + sizeof(int) * 64 + 16;
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 16 bytes global -> shared without a register round trip (all of a tile's rows are in flight at once); !valid: zeros
+__device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(n) : "memory");
+}
+
+// tanh to fp32 accuracy without the slow path of tanhf for the arguments a soft cap sees: |x| < 0.35 (a score of a third of
+// the cap) takes the odd Taylor polynomial up to x^9 (error below 2e-8), anything larger 1 - 2 / (exp(2x) + 1).
+__device__ __forceinline__ float tanh_f32(float x) {
+  const float x2 = x * x;
+  if (x2 < 0.1225f) return x * (1.0f + x2 * (-0.33333334f + x2 * (0.13333334f + x2 * (-0.05396825f + x2 * 0.02186949f))));
+  return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f);
 }
 
 template <int HPW, int DVT>
@@ -50,9 +64,10 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
   bf16* sK = sQ + kWmmaRows * QP;                     // [G][BN][KP]
   bf16* sV = sK + G * BN * KP;                        // [G][BN][VP]
   bf16* sP = sV + G * BN * VP;                        // [H][16][PP]
-  float* sTalk = reinterpret_cast<float*>(sP + H * kWmmaRows * PP);  // [H][H]
-  float* sPb = sTalk + H * H;                         // [H]
-  int* sRow = reinterpret_cast<int*>(sPb + H);        // [BN] cache row of each key of the tile (-1: none)
+  float* sTalk = reinterpret_cast<float*>(sP + H * kWmmaRows * PP);  // [H][HMAX]
+  float* sPb = sTalk + H * HMAX;                      // [H]
+  float* sBias = sPb + H;                             // [BN + 16][H] distance bias of the distances this tile can see
+  int* sRow = reinterpret_cast<int*>(sBias + (BN + kWmmaRows) * H);  // [BN] cache row of each key of the tile (-1: none)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, t4 = lane & 3;
   griddep_wait();
   const int tile = blockIdx.x, split = blockIdx.y;
@@ -63,14 +78,17 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
   const int kt_lo = split * per, kt_hi = (kt_lo + per < n_kt) ? kt_lo + per : n_kt;
   const int* pages = a.page_map + size_t(grp) * a.max_pages;
 
-  // stage Q (rows beyond the tile are zero), the mixing matrix and the head bias
-  for (int idx = tid; idx < kWmmaRows * (H * d / 8); idx += kWmmaThreads) {
-    const int row = idx / (H * d / 8), c8 = idx % (H * d / 8);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (row < nrows) v = *reinterpret_cast<const uint4*>(a.q + size_t(r0 + row) * H * d + c8 * 8);
-    *reinterpret_cast<uint4*>(sQ + row * QP + c8 * 8) = v;
+  // stage Q: only the tile's rows (the other rows of the MMA feed accumulator rows that are masked), the mixing matrix, the head bias
+  {
+    const int qch = H * d / 8;  // 16-byte chunks of a row
+    for (int row = 0; row < nrows; ++row)
+      for (int c8 = tid; c8 < qch; c8 += kWmmaThreads)
+        *reinterpret_cast<uint4*>(sQ + row * QP + c8 * 8) = *reinterpret_cast<const uint4*>(a.q + size_t(r0 + row) * H * d + c8 * 8);
   }
-  for (int e = tid; e < H * H; e += kWmmaThreads) sTalk[e] = a.talk ? a.talk[e] : ((e / H == e % H) ? 1.0f : 0.0f);
+  for (int e = tid; e < H * HMAX; e += kWmmaThreads) {
+    const int h = e / HMAX, g = e % HMAX;
+    sTalk[e] = g < H ? (a.talk ? a.talk[h * H + g] : (h == g ? 1.0f : 0.0f)) : 0.0f;
+  }
   for (int e = tid; e < H; e += kWmmaThreads) sPb[e] = a.head_bias ? a.head_bias[e] : 0.0f;
 
   float acc[HPW][DVT][4];
@@ -89,20 +107,44 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
       sRow[tid] = j <= khi ? pages[j / a.tokens_per_page] * a.tokens_per_page + j % a.tokens_per_page : -1;
     }
     __syncthreads();  // the previous tile's PV phase is over, the rows of this one are known
-    for (int idx = tid; idx < G * BN * (d / 8); idx += kWmmaThreads) {
-      const int c8 = idx % (d / 8), key = (idx / (d / 8)) % BN, c = idx / ((d / 8) * BN);
-      const int row = sRow[key];
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row >= 0) v = *reinterpret_cast<const uint4*>(a.k_pages + (size_t(c) * a.num_pages * a.tokens_per_page + row) * d + c8 * 8);
-      *reinterpret_cast<uint4*>(sK + (c * BN + key) * KP + c8 * 8) = v;
+    {
+      // the distances this tile's (row, key) pairs can have: p0 - (j0 + BN - 1) .. p0 + 15 - j0; slot n holds distance dist0 + n
+      const int dist0 = p0 - j0 - BN + 1;
+      for (int e = tid; e < (BN + kWmmaRows) * H; e += kWmmaThreads) {
+        const int dd = dist0 + e / H;
+        sBias[e] = (dd >= 0 && dd < a.window) ? __ldg(a.dist_bias + size_t(dd) * H + e % H) : 0.0f;
+      }
+      // K and V rows: thread t starts at (key, chunk) = (t / ch, t % ch) and walks 256 chunks further each time
+      const int kch = d / 8, vch = dv / 8;
+      const int kq = kWmmaThreads / kch, kr = kWmmaThreads % kch, vq = kWmmaThreads / vch, vr = kWmmaThreads % vch;
+      for (int c = 0; c < G; ++c) {
+        const bf16* kbase = a.k_pages + size_t(c) * a.num_pages * a.tokens_per_page * d;
+        bf16* kdst = sK + c * BN * KP;
+        for (int key = tid / kch, c8 = tid % kch; key < BN;) {
+          const int row = sRow[key];
+          cp_async_16(kdst + key * KP + c8 * 8, kbase + size_t(row < 0 ? 0 : row) * d + c8 * 8, row >= 0);
+          key += kq;
+          c8 += kr;
+          if (c8 >= kch) {
+            c8 -= kch;
+            ++key;
+          }
+        }
+        const bf16* vbase = a.v_pages + size_t(c) * a.num_pages * a.tokens_per_page * dv;
+        bf16* vdst = sV + c * BN * VP;
+        for (int key = tid / vch, c8 = tid % vch; key < BN;) {
+          const int row = sRow[key];
+          cp_async_16(vdst + key * VP + c8 * 8, vbase + size_t(row < 0 ? 0 : row) * dv + c8 * 8, row >= 0);
+          key += vq;
+          c8 += vr;
+          if (c8 >= vch) {
+            c8 -= vch;
+            ++key;
+          }
+        }
+      }
     }
-    for (int idx = tid; idx < G * BN * (dv / 8); idx += kWmmaThreads) {
-      const int c8 = idx % (dv / 8), key = (idx / (dv / 8)) % BN, c = idx / ((dv / 8) * BN);
-      const int row = sRow[key];
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row >= 0) v = *reinterpret_cast<const uint4*>(a.v_pages + (size_t(c) * a.num_pages * a.tokens_per_page + row) * dv + c8 * 8);
-      *reinterpret_cast<uint4*>(sV + (c * BN + key) * VP + c8 * 8) = v;
-    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
     // ---- S phase: this warp's 8 keys, every head ----
     if (warp * 8 < BN) {
@@ -123,12 +165,12 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
           }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int ir = g4 + (e >> 1) * 8, i = p0 + ir, j = j0 + warp * 8 + 2 * t4 + (e & 1);
+            const int ir = g4 + (e >> 1) * 8, jj = warp * 8 + 2 * t4 + (e & 1), dist = p0 + ir - j0 - jj;
             float wv = 0.0f;
-            if (ir < nrows && j <= i && i - j < a.window) {
+            if (ir < nrows && dist >= 0 && dist < a.window) {
               float sc = s[e] * a.scale;
-              if (a.softcap > 0.0f) sc = a.softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * sc * inv_cap) + 1.0f));  // cap * tanh(sc / cap)
-              sc += __ldg(a.dist_bias + size_t(i - j) * H + g) + sPb[g];
+              if (a.softcap > 0.0f) sc = a.softcap * tanh_f32(sc * inv_cap);
+              sc += sBias[(ir + BN - 1 - jj) * H + g] + sPb[g];
               wv = __fdividef(1.0f, 1.0f + __expf(-sc));
             }
             w[g][e] = wv;
@@ -139,13 +181,18 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
 #pragma unroll 1
       for (int h = 0; h < H; ++h) {
         float m[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        const float* tr = sTalk + h * H;
+        const float* tr = sTalk + h * HMAX;  // (rows padded to HMAX floats: 16-byte reads, zeros beyond H)
 #pragma unroll
-        for (int g = 0; g < HMAX; ++g) {
+        for (int g = 0; g < HMAX; g += 4) {
           if (g < H) {
-            const float tv = tr[g];
+            const float4 tv = *reinterpret_cast<const float4*>(tr + g);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) m[e] = fmaf(tv, w[g][e], m[e]);
+            for (int e = 0; e < 4; ++e) {
+              m[e] = fmaf(tv.x, w[g][e], m[e]);
+              if (g + 1 < H) m[e] = fmaf(tv.y, w[g + 1][e], m[e]);
+              if (g + 2 < H) m[e] = fmaf(tv.z, w[g + 2][e], m[e]);
+              if (g + 3 < H) m[e] = fmaf(tv.w, w[g + 3][e], m[e]);
+            }
           }
         }
         bf16* pb = sP + (h * kWmmaRows + g4) * PP + warp * 8 + 2 * t4;
