@@ -12,6 +12,7 @@
 #include "linear_any.cuh"
 #include "window_attention.cuh"
 #include "window_attention_mma.cuh"
+#include "window_attention_decode.cuh"
 #include "host_util.cuh"
 
 using namespace mtx;
@@ -211,6 +212,49 @@ int launch_window_mma(mtx_layered* e, const WindowAttnArgs<bf16>& wa, const Wind
   return launch(window_partial_sum_kernel, dim3(unsigned(blocks)), dim3(256), 0, st, (const float*)e->attn_part, wa.out, splits, per_split);
 }
 
+template <int CPW, int DT>
+int launch_window_decode_t(const WindowAttnArgs<bf16>& wa, const WindowDecodeExtra& x, size_t smem, cudaStream_t st) {
+  static size_t have = 0;  // per instantiation
+  if (smem > have) {
+    MTX_CUDA(cudaFuncSetAttribute(window_attention_decode_kernel<CPW, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    have = smem;
+  }
+  return launch(window_attention_decode_kernel<CPW, DT>, dim3(wa.rows, x.splits), dim3(kWdecThreads), smem, st, wa, x);
+}
+
+// the decode mixer (every row a token of its own sequence): (row, key split) work items, then the sum over the splits
+int launch_window_decode(mtx_layered* e, const WindowAttnArgs<bf16>& wa, const WindowDecodePlan& plan, cudaStream_t st) {
+  WindowDecodeExtra x;
+  x.partial = e->attn_part;
+  x.stages = plan.stages;
+  const int key_tiles = (wa.window + kWdecKeys - 1) / kWdecKeys;
+  // one wave: as many work items as CTAs fit on the GPU at once (a split's start-up -- its first tile's latency, the staging of
+  // the queries -- is worth several tiles, so more and shorter splits lose), at least four key tiles per split
+  size_t per_sm = (226 * 1024) / (plan.smem + 1024);
+  if (per_sm > 8) per_sm = 8;
+  int splits = int(per_sm) * e->num_sms / wa.rows;
+  if (splits > key_tiles / 4) splits = key_tiles / 4;
+  if (size_t(splits) * wa.rows > e->attn_part_rows) splits = int(e->attn_part_rows / wa.rows);
+  if (splits < 1) splits = 1;
+  x.splits = splits;
+  int rc = MTX_ERR_UNSUPPORTED;
+  if (plan.cpw == 1 && plan.dt == 4) rc = launch_window_decode_t<1, 4>(wa, x, plan.smem, st);
+  else if (plan.cpw == 1 && plan.dt == 8) rc = launch_window_decode_t<1, 8>(wa, x, plan.smem, st);
+  else if (plan.cpw == 1 && plan.dt == 16) rc = launch_window_decode_t<1, 16>(wa, x, plan.smem, st);
+  else if (plan.cpw == 2 && plan.dt == 4) rc = launch_window_decode_t<2, 4>(wa, x, plan.smem, st);
+  else if (plan.cpw == 2 && plan.dt == 8) rc = launch_window_decode_t<2, 8>(wa, x, plan.smem, st);
+  MTX_TRY(rc);
+  const long long per_split = (long long)wa.rows * wa.heads * wa.vdim;
+  long long blocks = (per_split / 2 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return launch(window_partial_sum_kernel, dim3(unsigned(blocks)), dim3(256), 0, st, (const float*)e->attn_part, wa.out, splits, per_split);
+}
+
+bool use_window_decode() {
+  static int on = env_int("MTX_WINDOW_DECODE", 1);
+  return on != 0;
+}
+
 template <typename T>
 int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
   const mtx_layered_config& c = e->cfg;
@@ -278,8 +322,13 @@ int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
     wa.softcap = l.softcap;
     bool done = false;
     if constexpr (sizeof(T) == 2) {
+      static const int force_stages = env_int("MTX_WINDOW_DECODE_STAGES", 0);
+      const WindowDecodePlan dplan = window_decode_plan(H, G, l.dim, l.vdim, force_stages);
       const WindowMmaPlan plan = window_mma_plan(H, G, l.dim, l.vdim);
-      if (plan.ok && b.n_tiles > 0 && b.tile_row0 != nullptr && use_window_mma()) {
+      if (dplan.ok && b.n_tiles == rows && b.tile_row0 != nullptr && use_window_mma() && use_window_decode()) {  // all single-row tiles
+        MTX_TRY(launch_window_decode(e, wa, dplan, st));
+        done = true;
+      } else if (plan.ok && b.n_tiles > 0 && b.tile_row0 != nullptr && use_window_mma()) {
         MTX_TRY(launch_window_mma(e, wa, plan, b, st));
         done = true;
       }

@@ -346,7 +346,7 @@ def _rms_err(got, want):
 
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,page", [
     (4, 2, 32, 16, 5, 4), (8, 8, 16, 48, 33, 16), (16, 4, 64, 64, 100, 8), (12, 3, 48, 32, 20, 4), (2, 1, 128, 128, 70, 16),
-    (1, 1, 16, 256, 9, 4), (4, 2, 96, 64, 40, 8)])
+    (1, 1, 16, 256, 9, 4), (4, 1, 96, 48, 40, 8)])
 def test_tensor_core_mixer_shapes_and_schedules(heads, kv_heads, dim, vdim, window, page):
   cfg = model([layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=window, ff=0, bias_max=float(window + 3)),
                layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=max(2, window // 2), ff=48)], width=64, vocab=90)
@@ -398,3 +398,26 @@ def test_tensor_core_mixer_window_edges(window, page):
     tail = [engine.step([(1, [tok], [0])]).cpu().double() for tok in toks[cut:]]
     engine.release_pages(1)
     assert _rms_err(torch.cat([head] + tail), want) < 2e-2, cut
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,page", [(8, 2, 64, 32, 150, 16), (6, 6, 32, 48, 97, 8), (16, 2, 16, 16, 260, 64)])
+def test_decode_mixer_key_splits_and_long_windows(heads, kv_heads, dim, vdim, window, page):
+  """Steps of single tokens only: the decode arm, windows of many 16-key tiles (several key splits, a ring of staged tiles that
+  wraps), three sequences of unequal length, one key far back made to dominate."""
+  cfg = model([layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=window, ff=0, bias_max=float(window)),
+               layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=window - 40, ff=32)], width=64, vocab=90)
+  t = ref.random_model(cfg, seed=31)
+  oracle = ref.KifusunRef(cfg, t)
+  lens = {"a": window + 90, "b": window - 3, "c": 21}
+  toks = {k: tokens_for(cfg, n, seed=n) for k, n in lens.items()}
+  want = {k: oracle.forward(v) for k, v in toks.items()}
+  engine, _ = make_engine(cfg, t, dtype="bfloat16", tokens_per_page=page, num_pages=3 * ((window + 90 + page - 1) // page) + 2, max_len=window + 100)
+  slot = {"a": 0, "b": 1, "c": 2}
+  got = {k: [] for k in toks}
+  for step in range(max(lens.values())):
+    live = [k for k in toks if step < lens[k]]
+    out = engine.step([(slot[k], [toks[k][step]], [0]) for k in live]).cpu().double()
+    for i, k in enumerate(live):
+      got[k].append(out[i : i + 1])
+  for k in toks:
+    assert _rms_err(torch.cat(got[k]), want[k]) < 2e-2, k
