@@ -1,4 +1,4 @@
-// Decode arm of the windowed sigmoid attention (window_attention.cuh has the contract): every row of the step is a single token
+// Decode arm of the windowed sigmoid attention (window_attention.cuh defines the operation): every row of the step is a single token
 // of its own sequence, so the kernel is bound by reading each row's window of K and V once.  bf16 operands.
 //
 // Work item = (row, key split); the key weights are not normalised, so the splits' fp32 partial outputs add (summed in a fixed

@@ -1,4 +1,4 @@
-// Tensor-core arm of the windowed sigmoid attention (window_attention.cuh has the contract and the row kernel), bf16 operands.
+// Tensor-core arm of the windowed sigmoid attention (window_attention.cuh defines the operation and has the row kernel), bf16 operands.
 //
 // Work item = (query tile, key split).  A query tile is up to 16 rows of ONE sequence with consecutive positions (a slice of a
 // prompt portion, or a single decoded token); the host passes the tile table.  Because the key weights are not normalised, the
