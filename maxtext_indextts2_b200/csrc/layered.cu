@@ -193,11 +193,24 @@ int launch_window_mma(mtx_layered* e, const WindowAttnArgs<bf16>& wa, const Wind
   x.partial = e->attn_part;
   x.n_tiles = b.n_tiles;
   x.bn = plan.bn;
+  x.hg = plan.hg;
   const int key_tiles = (wa.window + kWmmaRows - 1 + plan.bn - 1) / plan.bn;  // most key tiles a query tile can have
-  int splits = (2 * e->num_sms + b.n_tiles - 1) / b.n_tiles;
-  if (splits > key_tiles) splits = key_tiles;
-  if (size_t(splits) * wa.rows > e->attn_part_rows) splits = int(e->attn_part_rows / wa.rows);
-  if (splits < 1) splits = 1;
+  // key splits: enough work items to fill the SMs (one CTA each), at least two key tiles per split, and among the next few counts
+  // the one whose last wave is fullest (256 tiles x 2 splits on 148 SMs leave the fourth wave half empty; x 4 fill seven waves)
+  int cap = key_tiles / 2;
+  if (size_t(cap) * wa.rows > e->attn_part_rows) cap = int(e->attn_part_rows / wa.rows);
+  if (cap < 1) cap = 1;
+  int lo = (e->num_sms + b.n_tiles - 1) / b.n_tiles;
+  if (lo > cap) lo = cap;
+  int splits = lo;
+  double best = 0.0;
+  for (int sp = lo; sp <= cap && sp < lo + 8; ++sp) {
+    const double waves = double(b.n_tiles) * sp / e->num_sms, eff = waves / std::ceil(waves);
+    if (eff > best + 0.02) {
+      best = eff;
+      splits = sp;
+    }
+  }
   x.splits = splits;
   int rc = MTX_ERR_UNSUPPORTED;
   if (plan.hpw == 1 && plan.dvt == 8) rc = launch_window_mma_t<1, 8>(wa, x, plan.smem, st);

@@ -26,12 +26,14 @@ struct WindowMmaExtra {
   const int* tile_row0;  // [n_tiles + 1]
   float* partial;        // [splits, rows, H * dv]
   int n_tiles, splits, bn;
+  int hg;  // head groups of the S phase: 2 = two warps share a key group (bn = 32), each with half the heads; else 1
 };
 
-inline size_t window_mma_smem_bytes(int heads, int kv_heads, int dim, int vdim, int bn) {
+inline size_t window_mma_smem_bytes(int heads, int kv_heads, int dim, int vdim, int bn, int hg) {
   return size_t(2) * (size_t(kWmmaRows) * (heads * dim + 8) + size_t(kv_heads) * bn * (dim + 8) + size_t(kv_heads) * bn * (vdim + 8) +
                       size_t(heads) * kWmmaRows * (bn + 8)) +
-         sizeof(float) * (size_t(heads) * 16 + heads + size_t(bn + kWmmaRows) * heads) + sizeof(int) * 64 + 16;
+         sizeof(float) * (size_t(heads) * 16 + heads + size_t(bn + kWmmaRows) * heads + (hg == 2 ? size_t(heads) * 4 * 4 * bn : 0)) +
+         sizeof(int) * 64 + 16;
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
   float* sPb = sTalk + H * HMAX;                      // [H]
   float* sBias = sPb + H;                             // [BN + 16][H] distance bias of the distances this tile can see
   int* sRow = reinterpret_cast<int*>(sBias + (BN + kWmmaRows) * H);  // [BN] cache row of each key of the tile (-1: none)
+  float* sX = reinterpret_cast<float*>(sRow + 64);    // x.hg == 2: [H][4][4 * BN] raw weights, exchanged between the head groups
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, t4 = lane & 3;
   griddep_wait();
   const int tile = blockIdx.x, split = blockIdx.y;
@@ -130,6 +133,9 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
             ++key;
           }
         }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      for (int c = 0; c < G; ++c) {
         const bf16* vbase = a.v_pages + size_t(c) * a.num_pages * a.tokens_per_page * dv;
         bf16* vdst = sV + c * BN * VP;
         for (int key = tid / vch, c8 = tid % vch; key < BN;) {
@@ -143,43 +149,71 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
           }
         }
       }
+      asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // K has landed; V keeps flying under the S phase
     __syncthreads();
-    // ---- S phase: this warp's 8 keys, every head ----
-    if (warp * 8 < BN) {
+    // ---- S phase: this warp's 8 keys; every head, or (two head groups) its half of the heads ----
+    const int KG = BN >> 3, kg = warp % KG, hg = warp / KG;  // key group, head group
+    const int hpg = H / x.hg, h_lo = hg * hpg, h_hi = h_lo + hpg;
+    if (hg < x.hg) {
       float w[HMAX][4];
+      // the four weights of head g that this thread's accumulator elements hold: (rows g4, g4 + 8) x (keys 2 t4, 2 t4 + 1)
+      auto head_weights = [&](int g, float (&out)[4]) {
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const bf16* qb = sQ + g4 * QP + g * d + 2 * t4;
+        const bf16* kb = sK + ((g / rep) * BN + kg * 8 + g4) * KP + 2 * t4;
+        for (int ks = 0; ks < d; ks += 16) {
+          uint32_t af[4];
+          af[0] = *reinterpret_cast<const uint32_t*>(qb + ks);
+          af[1] = *reinterpret_cast<const uint32_t*>(qb + ks + 8 * QP);
+          af[2] = *reinterpret_cast<const uint32_t*>(qb + ks + 8);
+          af[3] = *reinterpret_cast<const uint32_t*>(qb + ks + 8 * QP + 8);
+          mma_bf16_16816(s, af, *reinterpret_cast<const uint32_t*>(kb + ks), *reinterpret_cast<const uint32_t*>(kb + ks + 8));
+        }
 #pragma unroll
-      for (int g = 0; g < HMAX; ++g) {
-        if (g < H) {
-          float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-          const bf16* qb = sQ + g4 * QP + g * d + 2 * t4;
-          const bf16* kb = sK + ((g / rep) * BN + warp * 8 + g4) * KP + 2 * t4;
-          for (int ks = 0; ks < d; ks += 16) {
-            uint32_t af[4];
-            af[0] = *reinterpret_cast<const uint32_t*>(qb + ks);
-            af[1] = *reinterpret_cast<const uint32_t*>(qb + ks + 8 * QP);
-            af[2] = *reinterpret_cast<const uint32_t*>(qb + ks + 8);
-            af[3] = *reinterpret_cast<const uint32_t*>(qb + ks + 8 * QP + 8);
-            mma_bf16_16816(s, af, *reinterpret_cast<const uint32_t*>(kb + ks), *reinterpret_cast<const uint32_t*>(kb + ks + 8));
+        for (int e = 0; e < 4; ++e) {
+          const int ir = g4 + (e >> 1) * 8, jj = kg * 8 + 2 * t4 + (e & 1), dist = p0 + ir - j0 - jj;
+          float wv = 0.0f;
+          if (ir < nrows && dist >= 0 && dist < a.window) {
+            float sc = s[e] * a.scale;
+            if (a.softcap > 0.0f) sc = a.softcap * tanh_f32(sc * inv_cap);
+            sc += sBias[(ir + BN - 1 - jj) * H + g] + sPb[g];
+            wv = __fdividef(1.0f, 1.0f + __expf(-sc));
           }
+          out[e] = wv;
+        }
+      };
+      if (x.hg == 2) {
+        // two warps share a key group: each computes the weights of half the heads, they meet in shared memory ([head][element]
+        // [thread of the key group]: conflict-free), and each mixes for its own half of the output heads
+        float* xw = sX + kg * 32 + lane;
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int ir = g4 + (e >> 1) * 8, jj = warp * 8 + 2 * t4 + (e & 1), dist = p0 + ir - j0 - jj;
-            float wv = 0.0f;
-            if (ir < nrows && dist >= 0 && dist < a.window) {
-              float sc = s[e] * a.scale;
-              if (a.softcap > 0.0f) sc = a.softcap * tanh_f32(sc * inv_cap);
-              sc += sBias[(ir + BN - 1 - jj) * H + g] + sPb[g];
-              wv = __fdividef(1.0f, 1.0f + __expf(-sc));
-            }
-            w[g][e] = wv;
+        for (int gl = 0; gl < HMAX / 2; ++gl) {
+          if (gl < hpg) {
+            float o[4];
+            head_weights(h_lo + gl, o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) xw[((h_lo + gl) * 4 + e) * (KG * 32)] = o[e];
           }
+        }
+        __syncthreads();  // (every warp is here: x.hg == 2 means KG * 2 == 8 warps)
+#pragma unroll
+        for (int g = 0; g < HMAX; ++g) {
+          if (g < H) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) w[g][e] = xw[(g * 4 + e) * (KG * 32)];
+          }
+        }
+      } else {
+#pragma unroll
+        for (int g = 0; g < HMAX; ++g) {
+          if (g < H) head_weights(g, w[g]);
         }
       }
       // mix the heads' weights; P_h as bf16
 #pragma unroll 1
-      for (int h = 0; h < H; ++h) {
+      for (int h = h_lo; h < h_hi; ++h) {
         float m[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         const float* tr = sTalk + h * HMAX;  // (rows padded to HMAX floats: 16-byte reads, zeros beyond H)
 #pragma unroll
@@ -195,11 +229,12 @@ __global__ void __launch_bounds__(kWmmaThreads, 1) window_attention_mma_kernel(c
             }
           }
         }
-        bf16* pb = sP + (h * kWmmaRows + g4) * PP + warp * 8 + 2 * t4;
+        bf16* pb = sP + (h * kWmmaRows + g4) * PP + kg * 8 + 2 * t4;
         *reinterpret_cast<uint32_t*>(pb) = pack_bf16x2(m[0], m[1]);
         *reinterpret_cast<uint32_t*>(pb + 8 * PP) = pack_bf16x2(m[2], m[3]);
       }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's part of V
     __syncthreads();
     // ---- PV phase: this warp's heads ----
 #pragma unroll
@@ -262,7 +297,7 @@ __global__ void window_partial_sum_kernel(const float* partial, bf16* out, int s
 
 struct WindowMmaPlan {
   bool ok = false;
-  int hpw = 0, dvt = 0, bn = 0;
+  int hpw = 0, dvt = 0, bn = 0, hg = 1;
   size_t smem = 0;
 };
 
@@ -275,10 +310,15 @@ inline WindowMmaPlan window_mma_plan(int heads, int kv_heads, int dim, int vdim)
   const int need = (vdim + 7) / 8;
   p.dvt = need <= 8 ? 8 : (need <= 16 ? 16 : 32);
   if (need > 32 || p.hpw * p.dvt > 32) return p;
-  for (int bn = 64; bn >= 32; bn /= 2) {
-    const size_t s = window_mma_smem_bytes(heads, kv_heads, dim, vdim, bn);
-    if (s <= 220 * 1024) {
-      p.bn = bn;
+  // 64-key tiles (every warp a key group of its own) if they fit; else 32-key tiles with the heads split over two warps per key
+  // group (an even head count, and room for the exchange buffer); else 32-key tiles with half the warps idle in the S phase
+  const int tries[3][2] = {{64, 1}, {32, 2}, {32, 1}};
+  for (const auto& t : tries) {
+    if (t[1] == 2 && heads % 2 != 0) continue;
+    const size_t s = window_mma_smem_bytes(heads, kv_heads, dim, vdim, t[0], t[1]);
+    if (s <= 227 * 1024) {  // the most a CTA can have
+      p.bn = t[0];
+      p.hg = t[1];
       p.smem = s;
       p.ok = true;
       return p;

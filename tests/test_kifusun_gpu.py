@@ -129,6 +129,19 @@ def test_portions_of_any_size(sizes):
   assert rel_err(torch.cat(got), want) < 2e-5
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 2e-2)])
+def test_a_step_longer_than_the_engine_takes_at_once_runs_in_slices(dtype, tol):
+  """max_step_rows = 10: a 37-token portion beside a 5-token one is cut into four device steps, inside both runs."""
+  cfg = model([layer(dim=32, vdim=16, window=9), layer(dim=32, vdim=16, window=20, ff=0)])
+  t = ref.random_model(cfg, seed=8)
+  oracle = ref.KifusunRef(cfg, t)
+  a, b = tokens_for(cfg, 37, seed=1), tokens_for(cfg, 5, seed=2)
+  engine, _ = make_engine(cfg, t, dtype=dtype, tokens_per_page=8, max_step_rows=10)
+  got = engine.step([(0, a, list(range(37))), (3, b, [0, 4])]).cpu().double()
+  want = torch.cat([oracle.forward(a), oracle.forward(b)[[0, 4]]])
+  assert (rel_err(got, want) if dtype == "float32" else _rms_err(got, want)) < tol
+
+
 def test_unequal_requests_in_one_batch_equal_each_alone_and_freed_pages_are_reused():
   cfg = DEFAULT()
   t = ref.random_model(cfg, seed=3)
@@ -346,7 +359,9 @@ def _rms_err(got, want):
 
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,page", [
     (4, 2, 32, 16, 5, 4), (8, 8, 16, 48, 33, 16), (16, 4, 64, 64, 100, 8), (12, 3, 48, 32, 20, 4), (2, 1, 128, 128, 70, 16),
-    (1, 1, 16, 256, 9, 4), (4, 1, 96, 48, 40, 8)])
+    (1, 1, 16, 256, 9, 4), (4, 1, 96, 48, 40, 8),
+    # heads too large for 64-key tiles: 32-key tiles, two warps per key group with half the heads each (8 + 8, and 3 + 3)
+    (16, 4, 128, 128, 70, 16), (6, 6, 256, 64, 40, 8)])
 def test_tensor_core_mixer_shapes_and_schedules(heads, kv_heads, dim, vdim, window, page):
   cfg = model([layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=window, ff=0, bias_max=float(window + 3)),
                layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=max(2, window // 2), ff=48)], width=64, vocab=90)
