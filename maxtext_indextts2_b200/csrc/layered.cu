@@ -34,7 +34,7 @@ struct mtx_layered {
   };
   std::vector<GraphEntry> graphs;
   cudaStream_t cap_stream = nullptr;
-  float* attn_part = nullptr;  // fp32 partial outputs of the attention's key splits: room for 2 * max_rows rows
+  float* attn_part = nullptr;  // fp32 partial outputs of the attention's key splits: room for 4 * max_rows rows
   size_t attn_part_rows = 0;
 };
 
@@ -67,7 +67,7 @@ LWs layered_layout(const mtx_layered* e) {
   L.act = take(R * (e->max_ff > 0 ? e->max_ff : 1) * es);
   L.wanted = take(W * c.width * es);
   L.obf = take(R * size_t(e->max_nqkv > c.width ? e->max_nqkv : c.width) * 2);  // bf16 output of a tcgen05 projection
-  L.attn_part = take(c.float32 ? 1024 : 2 * R * size_t(e->max_odim) * 4);
+  L.attn_part = take(c.float32 ? 1024 : 4 * R * size_t(e->max_odim) * 4);
   L.total = off;
   return L;
 }
@@ -454,7 +454,7 @@ int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes) {
   e->wanted = base + L.wanted;
   e->obf = base + L.obf;
   e->attn_part = reinterpret_cast<float*>(base + L.attn_part);
-  e->attn_part_rows = 2 * align_up(size_t(e->cfg.max_rows), 256);
+  e->attn_part_rows = 4 * align_up(size_t(e->cfg.max_rows), 256);
   e->bound = true;
   return MTX_OK;
 }
