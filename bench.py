@@ -388,7 +388,7 @@ def persistent_phase_times(lib, engine, B, sptr, L):
 
 def verify_step(engine, dparams, cfg, B):
   """Correctness gate of the timed run: ONE more decode step of the state the benchmark just timed, replayed for four slots
-  through the CPU oracle (as the checker; weights downloaded from the device, KV rows of those slots mirrored).  The GPU's
+  through the CPU oracle (as the reference; weights downloaded from the device, KV rows of those slots mirrored).  The GPU's
   greedy token must be the dtype-faithful oracle's argmax, or differ from it only at a near-tie (fp32-oracle margin between the
   two candidates in bf16 ulps of the top logit is reported)."""
   from oracle import mirror

@@ -995,7 +995,7 @@ int enqueue_step(mtx_engine* e, int mode, int rows, const int32_t* chunk_tokens,
       return launch(par_collect_kernel, sweep, dim3(kParThreads), 0, st, ps);
     }
     if (two_pass && cand_out != nullptr) {
-      // (MTX_PAR_COLLECT=0: the one-CTA-per-row extraction of round 1)
+      // (MTX_PAR_COLLECT=0: the earlier one-CTA-per-row extraction)
       ShardTopkArgs ta;
       memset(&ta, 0, sizeof(ta));
       ta.logits = e->s.logits;

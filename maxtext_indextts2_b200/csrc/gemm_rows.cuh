@@ -6,7 +6,7 @@
 //
 // The skinny kernel (gemm_umma.cuh) keeps the weights in the UMMA M dimension and the batch in N; its epilogue
 // thread owns ONE output feature and walks the rows, which is the right shape while a step has few rows and
-// costs a dependent chain per row when it has hundreds (76 us for the MLP-up GEMM at 256 rows, round 1).  Here the
+// costs a dependent chain per row when it has hundreds (76 us for the MLP-up GEMM at 256 rows).  Here the
 // roles are swapped: the ACTIVATIONS are the A operand, so a TMEM lane is a batch row and an epilogue thread owns
 // one row with its output features in consecutive columns:
 //   * RoPE partners (d +- D/2) and SwiGLU (gate, value) pairs are columns of the same thread: no shuffles, no

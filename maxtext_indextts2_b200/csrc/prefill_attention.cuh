@@ -3,7 +3,7 @@
 //
 // A prefill chunk is `rows` consecutive prompt positions [start_pos, start_pos + rows) of ONE sequence whose keys
 // and values (the rows of earlier chunks and, written by the QKV epilogue just before, this chunk's own) sit in the
-// prefill segment of one cache plane.  Round 1 ran every position as an independent decode row, so each of them
+// prefill segment of one cache plane.  The first version ran every position as an independent decode row, so each of them
 // streamed the whole prefix again (1 GB per layer for the last 256 positions of a 4k prompt).  Here the positions
 // share the key / value tiles:
 //

@@ -510,7 +510,7 @@ __global__ void __launch_bounds__(kSampleThreads) commit_topk_kernel(const Commi
 namespace mtx {
 
 // =============================================================================================================
-// top-k / nucleus over materialised logits on ALL SMs (round 2).  sample_rows_kernel above walks a row with one CTA
+// top-k / nucleus over materialised logits on ALL SMs.  sample_rows_kernel above walks a row with one CTA
 // (64 CTAs at batch 64, seven passes over 1 MB each: ~1.4 ms per step); here the same radix descent is cut along the
 // vocabulary: slices x ceil(rows / row_group) CTAs histogram their slice in shared memory and add the non-empty bins to
 // the row's global histogram, one small CTA per row picks the bin; three levels of 11 + 11 + 10 key bits, one sweep counts

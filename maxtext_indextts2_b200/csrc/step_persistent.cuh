@@ -2,7 +2,7 @@
 //
 // Why: as separate kernels every phase of a layer (QKV, attention, out-proj, MLP up, MLP down, two
 // norms) costs 8-16 us of launch / drain / dependency latency against 0.5-10 us of HBM time
-// (profiles/, round 1).  Here a phase boundary is one grid barrier (~1.3 us) and the HBM stream never
+// (profiles/).  Here a phase boundary is one grid barrier (~1.3 us) and the HBM stream never
 // stops at it: the weight producer of every CTA runs AHEAD of the barrier, pulling the next phases'
 // weight tiles into its shared-memory ring while the current phase drains (weights never depend on
 // activations); only the small activation tiles wait for the barrier.

@@ -96,7 +96,7 @@ class DeviceParams:
   """Weights in the layout of ``mtx_weights`` (include/mtx_b200.h), resident in HBM.
 
   `folded`: wqkv / w01 carry the RMSNorm scales of their input and attn_norm / mlp_norm are ones
-  (see :func:`fold_norm_scales`); `source` is then the unfolded original (kept for checkers), else None."""
+  (see :func:`fold_norm_scales`); `source` is then the unfolded original (kept for verification), else None."""
 
   def __init__(self, tensors: dict, folded: bool = False, source: "Optional[DeviceParams]" = None):
     self.tensors = tensors

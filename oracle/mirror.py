@@ -1,7 +1,7 @@
 """ORACLE helper -- copies the state of a CUDA ``MaxEngine`` into a ``DecodeOracle``.
 
 THIS IS TEST INFRASTRUCTURE, NOT PRODUCT CODE (see the header of ``decode_ref.py``): only
-``tests/``, ``__graft_entry__.smoke()`` and the checker legs of ``bench.py`` (``cpu_baseline``,
+``tests/``, ``__graft_entry__.smoke()`` and the verification legs of ``bench.py`` (``cpu_baseline``,
 ``--impl reference``, ``verify``) import it.
 
 Rows (decode slots) never interact inside a step (attentions.py:587-588 masks per slot), so an
