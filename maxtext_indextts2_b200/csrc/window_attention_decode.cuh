@@ -32,7 +32,7 @@ inline size_t window_decode_tile_bytes(int kv_heads, int dim, int vdim) {
 inline size_t window_decode_smem_bytes(int heads, int kv_heads, int dim, int vdim, int stages) {
   return size_t(2) * (size_t(kv_heads) * 8 * (dim + 8) + size_t(kv_heads) * 8 * (kWdecKeys + 8)) +
          size_t(stages) * window_decode_tile_bytes(kv_heads, dim, vdim) +
-         sizeof(float) * (size_t(kWdecKeys) * (heads + 1) + size_t(heads) * heads + heads) + 16;
+         sizeof(float) * (size_t(kWdecKeys) * (heads + 1) + size_t(heads) * heads + 2 * size_t(heads)) + 16;
 }
 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(kWdecThreads) window_attention_decode_kernel(c
   float* sW = reinterpret_cast<float*>(sV + size_t(NS) * G * kWdecKeys * VP);  // [16][WP] raw weights of the tile
   float* sTalk = sW + kWdecKeys * WP;                    // [H][H]
   float* sPb = sTalk + H * H;                            // [H]
+  int* sSlot = reinterpret_cast<int*>(sPb + H);          // [H] row of sP that holds head h: (h / rep) * 8 + h % rep
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, t4 = lane & 3;
   griddep_wait();
   const int r = blockIdx.x, split = blockIdx.y;
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(kWdecThreads) window_attention_decode_kernel(c
   const int n = kt_hi > kt_lo ? kt_hi - kt_lo : 0;
   const int* pages = a.page_map + size_t(grp) * a.max_pages;
   const size_t kv_rows = size_t(a.num_pages) * a.tokens_per_page;
+  const int tpp_shift = (a.tokens_per_page & (a.tokens_per_page - 1)) == 0 ? __ffs(a.tokens_per_page) - 1 : -1;
 
   // tile t of this split -> ring slot t % NS: thread (key = tid / 8, lane-of-key = tid % 8) copies every 8th 16-byte chunk of
   // its key's K and V rows of every kv head; keys beyond the row's own position are zero-filled (and masked below)
@@ -73,15 +75,23 @@ __global__ void __launch_bounds__(kWdecThreads) window_attention_decode_kernel(c
     const int st = t % NS, kk = tid >> 3, sub = tid & 7;
     const int j = klo + (kt_lo + t) * kWdecKeys + kk;
     const bool valid = j <= i;
-    const size_t row = valid ? size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page : 0;
+    const int pg = tpp_shift >= 0 ? j >> tpp_shift : j / a.tokens_per_page, in_pg = j - pg * a.tokens_per_page;
+    const size_t row = valid ? size_t(pages[pg]) * a.tokens_per_page + in_pg : 0;
     const int kch = d >> 3, vch = dv >> 3;
+    const bf16* ksrc = a.k_pages + row * d + sub * 8;
+    const bf16* vsrc = a.v_pages + row * dv + sub * 8;
+    uint32_t kdst = smem_u32(sK + (size_t(st) * G * kWdecKeys + kk) * QP + sub * 8);
+    uint32_t vdst = smem_u32(sV + (size_t(st) * G * kWdecKeys + kk) * VP + sub * 8);
+    const int nbytes = valid ? 16 : 0;
     for (int c = 0; c < G; ++c) {
-      const bf16* ksrc = a.k_pages + (size_t(c) * kv_rows + row) * d;
-      bf16* kdst = sK + ((size_t(st) * G + c) * kWdecKeys + kk) * QP;
-      for (int c8 = sub; c8 < kch; c8 += 8) cp_async_16(kdst + c8 * 8, ksrc + c8 * 8, valid);
-      const bf16* vsrc = a.v_pages + (size_t(c) * kv_rows + row) * dv;
-      bf16* vdst = sV + ((size_t(st) * G + c) * kWdecKeys + kk) * VP;
-      for (int c8 = sub; c8 < vch; c8 += 8) cp_async_16(vdst + c8 * 8, vsrc + c8 * 8, valid);
+      for (int c8 = sub; c8 < kch; c8 += 8)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst + (c8 - sub) * 16), "l"(ksrc + (c8 - sub) * 8), "r"(nbytes) : "memory");
+      for (int c8 = sub; c8 < vch; c8 += 8)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst + (c8 - sub) * 16), "l"(vsrc + (c8 - sub) * 8), "r"(nbytes) : "memory");
+      ksrc += kv_rows * d;
+      vsrc += kv_rows * dv;
+      kdst += kWdecKeys * QP * 2;
+      vdst += kWdecKeys * VP * 2;
     }
   };
   for (int s = 0; s < NS - 1; ++s) {
@@ -96,7 +106,10 @@ __global__ void __launch_bounds__(kWdecThreads) window_attention_decode_kernel(c
     *reinterpret_cast<uint4*>(sQ + slot * QP + c8 * 8) = v;
   }
   for (int e = tid; e < H * H; e += kWdecThreads) sTalk[e] = a.talk ? a.talk[e] : ((e / H == e % H) ? 1.0f : 0.0f);
-  for (int e = tid; e < H; e += kWdecThreads) sPb[e] = a.head_bias ? a.head_bias[e] : 0.0f;
+  for (int e = tid; e < H; e += kWdecThreads) {
+    sPb[e] = a.head_bias ? a.head_bias[e] : 0.0f;
+    sSlot[e] = (e / rep) * 8 + e % rep;
+  }
   for (int e = tid; e < G * 8 * PP; e += kWdecThreads) sP[e] = __float2bfloat16(0.0f);  // slots beyond rep stay zero
 
   float acc[CPW][DT][4];
@@ -120,6 +133,13 @@ __global__ void __launch_bounds__(kWdecThreads) window_attention_decode_kernel(c
       const int c = warp + 4 * u;
       if (c < G) {
         float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // this thread's four (key, head) elements: their distance biases are fetched before the MMA chain, which hides the loads
+        float db[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int hh = 2 * t4 + (e & 1), dist = i - (j0 + g4 + (e >> 1) * 8);
+          db[e] = (hh < rep && dist >= 0 && dist < a.window) ? __ldg(a.dist_bias + size_t(dist) * H + c * rep + hh) : 0.0f;
+        }
         const bf16* kb = sK + ((size_t(st) * G + c) * kWdecKeys + (lane & 7) + ((lane >> 3) & 1) * 8) * QP + (lane >> 4) * 8;
         const bf16* qb = sQ + (c * 8 + g4) * QP + 2 * t4;
 #pragma unroll 4
@@ -139,7 +159,7 @@ __global__ void __launch_bounds__(kWdecThreads) window_attention_decode_kernel(c
             if (dist >= 0 && dist < a.window) {
               float sc = s[e] * a.scale;
               if (a.softcap > 0.0f) sc = a.softcap * tanh_f32(sc * inv_cap);
-              sc += __ldg(a.dist_bias + size_t(dist) * H + g) + sPb[g];
+              sc += db[e] + sPb[g];
               wv = __fdividef(1.0f, 1.0f + __expf(-sc));
             }
             sW[kk * WP + g] = wv;
@@ -149,14 +169,16 @@ __global__ void __launch_bounds__(kWdecThreads) window_attention_decode_kernel(c
     }
     __syncthreads();
     // ---- mix the heads' weights ----
-    for (int o = tid; o < kWdecKeys * H; o += kWdecThreads) {
-      const int kk = o & (kWdecKeys - 1), h = o / kWdecKeys;
-      const float* tr = sTalk + h * H;
+    {
+      const int kk = tid & (kWdecKeys - 1);  // (128 threads = 8 heads x 16 keys per pass)
       const float* wr = sW + kk * WP;
-      float m = 0.0f;
+      for (int h = tid >> 4; h < H; h += kWdecThreads / kWdecKeys) {
+        const float* tr = sTalk + h * H;
+        float m = 0.0f;
 #pragma unroll 4
-      for (int g = 0; g < H; ++g) m = fmaf(tr[g], wr[g], m);
-      sP[((h / rep) * 8 + h % rep) * PP + kk] = __float2bfloat16(m);
+        for (int g = 0; g < H; ++g) m = fmaf(tr[g], wr[g], m);
+        sP[sSlot[h] * PP + kk] = __float2bfloat16(m);
+      }
     }
     __syncthreads();
     // ---- PV phase ----
