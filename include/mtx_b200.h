@@ -360,6 +360,76 @@ int mtx_engine_rebind_state(mtx_engine* e, const mtx_decode_state* s);
  * the cache fp32 too (weights are then fp32 arrays), 0 keeps them bfloat16 with fp32 accumulation. */
 
 #define MTX_MIXER_WINDOW_SIGMOID 1 /* csrc/window_attention.cuh */
+#define MTX_MIXER_COMPOSITE 2      /* a softmax attention and / or a linear recurrence that read the same input; their outputs are
+                                      concatenated (each times its out_scale) and share one output projection, so the result is
+                                      out_scale_a * attention + out_scale_r * recurrence.  csrc/softmax_attention.cuh,
+                                      csrc/recurrent_mixers.cuh */
+
+#define MTX_NORM_OUT_GAIN 0 /* x += gain * unit(sub(x)): the sublayer reads x itself, one gain on its output */
+#define MTX_NORM_SANDWICH 1 /* x += wnorm(sub(wnorm(x, pre)), post) with wnorm(y, w) = unit(y) * (1 + w), weights [width] */
+
+#define MTX_FF_GELU_GATED 0    /* down(gelu_tanh(gate x) * up x) */
+#define MTX_FF_CLAMPED_GATED 1 /* down(g s(1.702 g) (u + 1)), g = min(gate x, limit), u = clamp(up x, -limit, limit), s = sigmoid */
+#define MTX_FF_MOE 2           /* routed experts of the clamped form plus an optional shared one (mtx_moe_desc) */
+
+/* Causal softmax attention over the paged cache (csrc/softmax_attention.cuh).  Its projection rows in the layer's w_in are
+ * [q: heads*dim | k: kv_heads*dim | v: kv_heads*vdim unless values_are_keys]. */
+typedef struct {
+  int32_t heads;           /* 0: the layer has no softmax attention */
+  int32_t kv_heads;        /* query head h reads key head h / (heads / kv_heads) */
+  int32_t dim, vdim;
+  int32_t window;          /* a query at i sees i - window < j <= i; 0: every j <= i */
+  int32_t rot_dims;        /* leading channels of each head that turn with the position, paired (2i, 2i + 1); 0: none */
+  int32_t values_are_keys; /* 1: the value of a token is its key as projected (before the rotation); needs vdim == dim */
+  float scale;             /* multiplies <q, k> */
+  float out_scale;
+  const float* rot_freq;   /* [rot_dims / 2] radians per position of pair i */
+  void* k_pages;           /* [kv_heads, num_pages, tokens_per_page, dim] */
+  void* v_pages;           /* [kv_heads, num_pages, tokens_per_page, vdim] */
+} mtx_softmax_attn_desc;
+
+#define MTX_REC_GLA 1   /* S = diag(a) S + k v^T, o = S^T q, a = sigmoid(z)^(1 / tau) per key channel, z = low-rank projection */
+#define MTX_REC_MLSTM 2 /* S = e^(f + m' - m) S + e^(i - m) k v^T, n likewise with k alone, m = max(f + m', i) from m = 0;
+                           o = S^T q / (max(|n.q|, e^-m) + denom_eps); i = cap tanh(./cap), f = logsigmoid(cap tanh(./cap)) */
+
+/* A linear recurrence with a matrix state per head (csrc/recurrent_mixers.cuh).  State, decays and gates are fp32.  Its
+ * projection rows in w_in follow the attention's: [q: heads*dim | k: heads*dim | v: heads*vdim | output gate: heads*vdim |
+ * GLA: decay_rank rows of the decay's down-projection; mLSTM: heads input-gate rows then heads forget-gate rows]. */
+typedef struct {
+  int32_t kind;            /* 0: the layer has no recurrence */
+  int32_t heads, dim, vdim;
+  int32_t decay_rank;      /* GLA */
+  int32_t gate_silu;       /* output gate: 1 silu, 0 sigmoid */
+  float q_scale;           /* multiplies q */
+  float tau;               /* GLA */
+  float gate_cap;          /* mLSTM */
+  float denom_eps;         /* mLSTM */
+  float out_scale;
+  const float* decay_up_t; /* GLA: [decay_rank, heads*dim] (the up-projection, transposed) */
+  const float* decay_bias; /* GLA: [heads*dim] */
+  const float* gate_bias;  /* mLSTM: [2*heads] input gates, then forget gates */
+  const float* out_norm;   /* [heads*vdim]: o is divided by its per-head root mean square, then multiplied by this */
+  float* state_s;          /* [state slots, heads, dim, vdim] */
+  float* state_n;          /* mLSTM: [state slots, heads, dim] */
+  float* state_m;          /* mLSTM: [state slots, heads] */
+} mtx_recurrent_desc;
+
+/* Routed feed-forward (csrc/moe.cuh): scores s = sigmoid(router x); an expert is chosen by s + correction among the experts of
+ * the keep_groups best groups (a group = experts / groups neighbours, scored by the sum of its two largest choice scores), the
+ * `top` largest; the chosen experts' outputs are weighted by s / (sum of the chosen s + 1e-20).  shared_ff > 0 adds an expert
+ * that every row uses. */
+typedef struct {
+  int32_t experts, top, groups, keep_groups;
+  int32_t ff;              /* hidden size of one expert */
+  int32_t shared_ff;
+  float limit, shared_limit;
+  const void* w_router;    /* [experts, width] */
+  const float* correction; /* [experts] or NULL */
+  const void* w_gate_up;   /* [experts, 2*ff, width], rows interleaved as in mtx_layer_desc.w_gate_up */
+  const void* w_down;      /* [experts, width, ff] */
+  const void* shared_gate_up; /* [2*shared_ff, width] */
+  const void* shared_down;    /* [width, shared_ff] */
+} mtx_moe_desc;
 
 typedef struct {
   int32_t mixer;        /* MTX_MIXER_* */
@@ -369,7 +439,7 @@ typedef struct {
   int32_t vdim;         /* per-head size of values */
   int32_t window;       /* a query at position i sees the keys j with 0 <= i - j < window */
   int32_t value_mix;    /* 0 none; 1 this layer's values are kept for later layers; 2 v = (1 - lambda) v + lambda kept */
-  int32_t ff;           /* hidden size of the gated feed-forward; 0 = the layer has none */
+  int32_t ff;           /* hidden size of the gated feed-forward; 0 = the layer has none (MTX_FF_MOE: see moe) */
   float scale;          /* multiplies <q, k> */
   float softcap;        /* cap * tanh(score / cap); 0 = off */
   float value_lambda;
@@ -381,21 +451,39 @@ typedef struct {
   const float* dist_bias; /* [window, H]: added to the score of the key at distance i - j */
   const float* head_bias; /* [H] or NULL */
   const float* talk;    /* [H, H] mixing of the heads' weights, or NULL */
-  const void* wo;       /* [width, H*vdim] */
+  const void* wo;       /* [width, H*vdim]; MTX_MIXER_COMPOSITE: [width, attn.heads*attn.vdim + rec.heads*rec.vdim] */
   const void* w_gate_up; /* [2*ff, width], rows interleaved: 2f = gate f, 2f + 1 = up f */
   const void* w_down;   /* [width, ff] */
   void* k_pages;        /* [G, num_pages, tokens_per_page, dim] */
   void* v_pages;        /* [G, num_pages, tokens_per_page, vdim] */
+  /* -- the fields above describe MTX_MIXER_WINDOW_SIGMOID layers with MTX_NORM_OUT_GAIN; the ones below every other kind -- */
+  int32_t norm_style;   /* MTX_NORM_* */
+  int32_t ff_kind;      /* MTX_FF_* */
+  int32_t n_in;         /* MTX_MIXER_COMPOSITE: rows of w_in (the sub-mixers' rows, then zero rows up to a tile edge if any) */
+  int32_t add_embedding; /* 1: before this layer x += the embedding output of the same row */
+  float ff_limit;       /* MTX_FF_CLAMPED_GATED */
+  const float* norm1;   /* MTX_NORM_SANDWICH: weights [width] before / after the mixer (norm1, norm1b) ... */
+  const float* norm1b;
+  const float* norm2;   /* ... and before / after the feed-forward */
+  const float* norm2b;
+  const float* add_vector; /* [width] or NULL: before this layer (after add_embedding) x += add_vector */
+  const void* w_in;     /* MTX_MIXER_COMPOSITE: [n_in, width] all projections of the mixer's input */
+  const float* b_in;    /* [n_in] or NULL */
+  const float* bo;      /* [width] bias of the output projection, already scaled, or NULL */
+  mtx_softmax_attn_desc attn;
+  mtx_recurrent_desc rec;
+  mtx_moe_desc moe;
 } mtx_layer_desc;
 
 typedef struct {
-  int32_t num_layers;
+  int32_t num_layers;          /* layer RUNS: a layer that runs twice (a loop) is listed twice, with the same weights and its
+                                  own page pools and state */
   int32_t width;
   int32_t vocab;
   int32_t float32;             /* 1: true fp32 everywhere */
   int32_t max_rows;            /* most rows of one step */
   int32_t max_want;            /* most rows of one step whose logits are asked for */
-  int32_t num_groups;          /* page groups (decode slots) */
+  int32_t num_groups;          /* page groups (decode slots) = rows of the page map = state slots */
   int32_t num_pages;
   int32_t tokens_per_page;
   int32_t max_pages_per_group;
@@ -404,6 +492,8 @@ typedef struct {
   float final_gain;
   const void* embedding;       /* [vocab, width] */
   const void* head;            /* [vocab, width] */
+  const float* final_norm;     /* NULL: the final norm has the single gain final_gain; else weights [width], unit(x) * (1 + w) */
+  float logit_softcap;         /* cap * tanh(logits / cap); 0 = off */
 } mtx_layered_config;
 
 typedef struct {
@@ -419,6 +509,11 @@ typedef struct {
    * tile_row0[t + 1]): at most 16 rows of ONE group with consecutive positions; the tiles cover every row once. */
   int32_t n_tiles;
   const int32_t* tile_row0;    /* [n_tiles + 1] */
+  /* The rows cut into runs: run r = rows [run_row0[r], run_row0[r + 1]) of ONE group with consecutive positions, at most one
+   * run per group.  Recurrent mixers walk a run in order from the group's state (zero when the run starts at position 0) and
+   * leave the state after its last row.  Needed by models with MTX_MIXER_COMPOSITE layers. */
+  int32_t n_runs;
+  const int32_t* run_row0;     /* [n_runs + 1] */
 } mtx_ragged_batch;
 
 typedef struct mtx_layered mtx_layered; /* opaque */

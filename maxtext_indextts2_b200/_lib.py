@@ -108,7 +108,40 @@ class DecodeState(ctypes.Structure):
   ]
 
 
-MIXER_WINDOW_SIGMOID = 1
+MIXER_WINDOW_SIGMOID, MIXER_COMPOSITE = 1, 2
+NORM_OUT_GAIN, NORM_SANDWICH = 0, 1
+FF_GELU_GATED, FF_CLAMPED_GATED, FF_MOE = 0, 1, 2
+REC_GLA, REC_MLSTM = 1, 2
+
+
+class SoftmaxAttnDesc(ctypes.Structure):
+  """mtx_softmax_attn_desc."""
+
+  _fields_ = (
+      [(n, ctypes.c_int32) for n in ("heads", "kv_heads", "dim", "vdim", "window", "rot_dims", "values_are_keys")]
+      + [(n, ctypes.c_float) for n in ("scale", "out_scale")]
+      + [(n, ctypes.c_void_p) for n in ("rot_freq", "k_pages", "v_pages")]
+  )
+
+
+class RecurrentDesc(ctypes.Structure):
+  """mtx_recurrent_desc."""
+
+  _fields_ = (
+      [(n, ctypes.c_int32) for n in ("kind", "heads", "dim", "vdim", "decay_rank", "gate_silu")]
+      + [(n, ctypes.c_float) for n in ("q_scale", "tau", "gate_cap", "denom_eps", "out_scale")]
+      + [(n, ctypes.c_void_p) for n in ("decay_up_t", "decay_bias", "gate_bias", "out_norm", "state_s", "state_n", "state_m")]
+  )
+
+
+class MoeDesc(ctypes.Structure):
+  """mtx_moe_desc."""
+
+  _fields_ = (
+      [(n, ctypes.c_int32) for n in ("experts", "top", "groups", "keep_groups", "ff", "shared_ff")]
+      + [(n, ctypes.c_float) for n in ("limit", "shared_limit")]
+      + [(n, ctypes.c_void_p) for n in ("w_router", "correction", "w_gate_up", "w_down", "shared_gate_up", "shared_down")]
+  )
 
 
 class LayerDesc(ctypes.Structure):
@@ -119,6 +152,10 @@ class LayerDesc(ctypes.Structure):
       + [(n, ctypes.c_float) for n in ("scale", "softcap", "value_lambda", "gain1", "gain2")]
       + [(n, ctypes.c_void_p) for n in ("wqkv", "bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk", "wo", "w_gate_up", "w_down",
                                         "k_pages", "v_pages")]
+      + [(n, ctypes.c_int32) for n in ("norm_style", "ff_kind", "n_in", "add_embedding")]
+      + [("ff_limit", ctypes.c_float)]
+      + [(n, ctypes.c_void_p) for n in ("norm1", "norm1b", "norm2", "norm2b", "add_vector", "w_in", "b_in", "bo")]
+      + [("attn", SoftmaxAttnDesc), ("rec", RecurrentDesc), ("moe", MoeDesc)]
   )
 
 
@@ -129,7 +166,8 @@ class LayeredConfig(ctypes.Structure):
       [(n, ctypes.c_int32) for n in ("num_layers", "width", "vocab", "float32", "max_rows", "max_want", "num_groups", "num_pages",
                                      "tokens_per_page", "max_pages_per_group")]
       + [(n, ctypes.c_float) for n in ("eps", "embed_scale", "final_gain")]
-      + [(n, ctypes.c_void_p) for n in ("embedding", "head")]
+      + [(n, ctypes.c_void_p) for n in ("embedding", "head", "final_norm")]
+      + [("logit_softcap", ctypes.c_float)]
   )
 
 
@@ -138,7 +176,7 @@ class RaggedBatch(ctypes.Structure):
 
   _fields_ = [("rows", ctypes.c_int32), ("token", ctypes.c_void_p), ("group", ctypes.c_void_p), ("pos", ctypes.c_void_p),
               ("page_map", ctypes.c_void_p), ("n_want", ctypes.c_int32), ("want_rows", ctypes.c_void_p), ("logits", ctypes.c_void_p),
-              ("n_tiles", ctypes.c_int32), ("tile_row0", ctypes.c_void_p)]
+              ("n_tiles", ctypes.c_int32), ("tile_row0", ctypes.c_void_p), ("n_runs", ctypes.c_int32), ("run_row0", ctypes.c_void_p)]
 
 
 def sources() -> list[str]:

@@ -5,6 +5,10 @@
 //                           values an earlier layer computed for the same token, append of k and v to the paged cache
 //   norm_residual_kernel    x += gain * y / sqrt(mean(y^2) + eps)   (a normalisation with ONE gain, on the sublayer's OUTPUT)
 //   scalar_norm_rows_kernel n = gain * x[row] / sqrt(mean(x[row]^2) + eps) for a gathered subset of rows (before the logits)
+//   sandwich_step_kernel    norms with a weight vector stored around zero, before AND after a sublayer:
+//                           x += wnorm(y + bias, post); x += embedding output; x += vector; xa = wnorm(x, pre)   (each part optional)
+//                           with wnorm(y, w) = y / sqrt(mean(y^2) + eps) * (1 + w)
+//   weighted_norm_rows_kernel  wnorm of a gathered subset of rows;  softcap_kernel  z = cap * tanh(z / cap)
 //
 // Everything here is fp32 arithmetic; T is the dtype the matrix products and the cache use (bf16, or float for a float32 engine).
 #pragma once
@@ -32,8 +36,9 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return r;
 }
 
+// (x0: a second copy of the embedding output for layers that add it again, or null)
 template <typename T>
-__global__ void embed_rows_kernel(const int* token, const T* embedding, int vocab, float scale, float* x, T* xa, int width) {
+__global__ void embed_rows_kernel(const int* token, const T* embedding, int vocab, float scale, float* x, T* xa, int width, float* x0) {
   griddep_wait();
   const int r = blockIdx.x;
   int tok = token[r];
@@ -42,7 +47,88 @@ __global__ void embed_rows_kernel(const int* token, const T* embedding, int voca
     const float v = act_f32(embedding[size_t(tok) * width + c]) * scale;
     x[size_t(r) * width + c] = v;
     xa[size_t(r) * width + c] = to_act<T>(v);
+    if (x0) x0[size_t(r) * width + c] = v;
   }
+}
+
+struct SandwichArgs {
+  const float* y;         // [rows, width] the sublayer's output, or null: no residual update in this call
+  const float* y_bias;    // [width] added to y before its norm, or null
+  const float* post;      // [width] weight of the norm on y
+  const float* x0;        // [rows, width] added to x after the update, or null
+  const float* add_vec;   // [width] added to x after that, or null
+  const float* pre;       // [width] weight of the norm whose result goes to xa, or null: xa is not written
+  float* x;               // [rows, width]
+  float eps;
+  int width;
+};
+
+// one CTA per row; the row of x stays in registers between the two reductions (width <= 256 * kSandwichMax)
+constexpr int kSandwichMax = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256) sandwich_step_kernel(const SandwichArgs a, T* xa) {
+  __shared__ float red[8];
+  griddep_wait();
+  const int r = blockIdx.x, W = a.width;
+  float* xr = a.x + size_t(r) * W;
+  float xv[kSandwichMax];
+  float f = 0.0f;
+  if (a.y) {
+    const float* yr = a.y + size_t(r) * W;
+    float ss = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kSandwichMax; ++u) {
+      const int c = threadIdx.x + u * 256;
+      if (c < W) {
+        const float v = yr[c] + (a.y_bias ? a.y_bias[c] : 0.0f);
+        ss = fmaf(v, v, ss);
+      }
+    }
+    ss = block_sum(ss, red);
+    f = 1.0f / sqrtf(ss / float(W) + a.eps);
+  }
+  float ss2 = 0.0f;
+#pragma unroll
+  for (int u = 0; u < kSandwichMax; ++u) {
+    const int c = threadIdx.x + u * 256;
+    if (c < W) {
+      float v = xr[c];
+      if (a.y) v += (a.y[size_t(r) * W + c] + (a.y_bias ? a.y_bias[c] : 0.0f)) * f * (1.0f + a.post[c]);
+      if (a.x0) v += a.x0[size_t(r) * W + c];
+      if (a.add_vec) v += a.add_vec[c];
+      xv[u] = v;
+      ss2 = fmaf(v, v, ss2);
+      if (a.y || a.x0 || a.add_vec) xr[c] = v;
+    }
+  }
+  if (!a.pre) return;
+  ss2 = block_sum(ss2, red);
+  const float f2 = 1.0f / sqrtf(ss2 / float(W) + a.eps);
+#pragma unroll
+  for (int u = 0; u < kSandwichMax; ++u) {
+    const int c = threadIdx.x + u * 256;
+    if (c < W) xa[size_t(r) * W + c] = to_act<T>(xv[u] * f2 * (1.0f + a.pre[c]));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) weighted_norm_rows_kernel(const float* x, const int* rows, const float* w, float eps, T* out, int width) {
+  __shared__ float red[8];
+  griddep_wait();
+  const int src = rows ? rows[blockIdx.x] : int(blockIdx.x);
+  const float* xr = x + size_t(src) * width;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(xr[c], xr[c], ss);
+  ss = block_sum(ss, red);
+  const float f = 1.0f / sqrtf(ss / float(width) + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) out[size_t(blockIdx.x) * width + c] = to_act<T>(xr[c] * f * (1.0f + w[c]));
+}
+
+__global__ void softcap_kernel(float* z, float cap, long long total) {
+  griddep_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    z[i] = cap * tanhf(z[i] / cap);
 }
 
 template <typename T>

@@ -1,7 +1,8 @@
 // The layered engine of include/mtx_b200.h (mtx_layered_*): a decoder given as a list of layer descriptors, stepped over ragged
-// batches whose keys and values live in page pools.  Host code only: the kernels are in linear_any.cuh (any-shape projections),
-// gemm_rows.cuh (the tcgen05 projections, for shapes made of whole 128 x 64 tiles), layer_ops.cuh (norms, residual, cache
-// append) and window_attention.cuh / window_attention_mma.cuh (the mixer).
+// batches whose keys and values live in page pools.  Host code only: the kernels are in linear_any.cuh (any-shape projections, also
+// grouped by expert), gemm_rows.cuh (the tcgen05 projections, for shapes made of whole 128 x 64 tiles), layer_ops.cuh (norms,
+// residual, cache append), window_attention*.cuh (the sigmoid window mixer), softmax_attention.cuh (causal softmax attention with
+// rotary positions), recurrent_mixers.cuh (GLA and mLSTM over state slots) and moe.cuh (routing).
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -13,6 +14,9 @@
 #include "window_attention.cuh"
 #include "window_attention_mma.cuh"
 #include "window_attention_decode.cuh"
+#include "softmax_attention.cuh"
+#include "recurrent_mixers.cuh"
+#include "moe.cuh"
 #include "host_util.cuh"
 
 using namespace mtx;
@@ -36,6 +40,12 @@ struct mtx_layered {
   cudaStream_t cap_stream = nullptr;
   float* attn_part = nullptr;  // fp32 partial outputs of the attention's key splits: room for 4 * max_rows rows
   size_t attn_part_rows = 0;
+  // composite mixers, sandwich norms, routed feed-forwards
+  bool sandwich = false;
+  int max_rec_o = 0, max_rec_aux = 0, max_moe_top = 0, max_moe_experts = 0, max_moe_ff = 0;
+  float *x0 = nullptr, *rec_o = nullptr, *rec_aux = nullptr, *moe_logits = nullptr, *moe_weight = nullptr, *moe_y = nullptr;
+  int *moe_chosen = nullptr, *moe_slot = nullptr, *moe_row = nullptr, *moe_off = nullptr;
+  void* moe_act = nullptr;
 };
 
 namespace {
@@ -44,6 +54,7 @@ size_t elem(const mtx_layered* e) { return e->cfg.float32 ? 4 : 2; }
 
 struct LWs {
   size_t x, y, qkv, v_shared, xa, q, attn, act, wanted, obf, attn_part, total;
+  size_t x0, rec_o, rec_aux, moe_logits, moe_weight, moe_y, moe_chosen, moe_slot, moe_row, moe_off, moe_act;
 };
 
 LWs layered_layout(const mtx_layered* e) {
@@ -68,6 +79,18 @@ LWs layered_layout(const mtx_layered* e) {
   L.wanted = take(W * c.width * es);
   L.obf = take(R * size_t(e->max_nqkv > c.width ? e->max_nqkv : c.width) * 2);  // bf16 output of a tcgen05 projection
   L.attn_part = take(c.float32 ? 1024 : 4 * R * size_t(e->max_odim) * 4);
+  L.x0 = take(e->sandwich ? R * c.width * 4 : 4);
+  L.rec_o = take(R * size_t(e->max_rec_o > 0 ? e->max_rec_o : 1) * 4);
+  L.rec_aux = take(R * size_t(e->max_rec_aux > 0 ? e->max_rec_aux : 1) * 4);
+  const size_t RT = R * size_t(e->max_moe_top > 0 ? e->max_moe_top : 0);  // (row, choice) entries
+  L.moe_logits = take(R * size_t(e->max_moe_experts > 0 ? e->max_moe_experts : 1) * 4);
+  L.moe_weight = take((RT + 1) * 4);
+  L.moe_y = take((RT * c.width + 1) * 4);
+  L.moe_chosen = take((RT + 1) * 4);
+  L.moe_slot = take((RT + 1) * 4);
+  L.moe_row = take((RT + 1) * 4);
+  L.moe_off = take(size_t(e->max_moe_experts + 2) * 4);
+  L.moe_act = take((RT * size_t(e->max_moe_ff) + 1) * es);
   L.total = off;
   return L;
 }
@@ -85,28 +108,31 @@ __global__ void bf16_rows_to_f32_kernel(const bf16* src, const float* bias, floa
     dst[i] = __bfloat162float(src[i]) + (bias ? bias[i % n] : 0.0f);
 }
 
-__global__ void gate_up_bf16_kernel(const bf16* src, bf16* act, int ff, long long total) {
+// (limit > 0: the clamped form g sigmoid(1.702 g) (u + 1); else gelu_tanh(g) u)
+__global__ void gate_up_bf16_kernel(const bf16* src, bf16* act, int ff, long long total, float limit) {
   griddep_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / ff, f = i % ff;
     const float g = __bfloat162float(src[r * 2 * ff + 2 * f]), u = __bfloat162float(src[r * 2 * ff + 2 * f + 1]);
-    act[i] = __float2bfloat16_rn(gelu_tanh_f(g) * u);
+    act[i] = __float2bfloat16_rn(limit > 0.0f ? clamped_gate_f(g, u, limit) : gelu_tanh_f(g) * u);
   }
 }
 
 // out (fp32, or the gated activation) = EPI(a[rows, k] . w[n, k]^T)
 template <typename T, int EPI>
-int run_linear(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st) {
+int run_linear(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st,
+               float limit = 0.0f) {
   if (rows <= 0) return MTX_OK;
   LinArgs<T> p;
   memset(&p, 0, sizeof(p));
+  p.limit = limit;
   p.a = static_cast<const T*>(a);
   p.w = static_cast<const T*>(w);
   p.bias = bias;
   p.out = out;
   p.act = static_cast<T*>(act);
   p.lda = k;
-  p.ldo = EPI == LIN_GATED ? n / 2 : n;
+  p.ldo = (EPI == LIN_GATED || EPI == LIN_GATED_CLAMP) ? n / 2 : n;
   p.rows = rows;
   p.n = n;
   p.k = k;
@@ -131,23 +157,53 @@ int run_umma_raw(mtx_layered* e, const void* a, const void* w, int rows, int n, 
 
 // ... then the epilogue as a row kernel
 template <int EPI>
-int run_linear_umma(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st) {
+int run_linear_umma(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st,
+                    float limit = 0.0f) {
   MTX_TRY(run_umma_raw(e, a, w, rows, n, k, st));
   const bf16* tmp = static_cast<const bf16*>(e->obf);
-  const long long total = (long long)rows * (EPI == LIN_GATED ? n / 2 : n);
+  constexpr bool gated = EPI == LIN_GATED || EPI == LIN_GATED_CLAMP;
+  const long long total = (long long)rows * (gated ? n / 2 : n);
   const int blocks = int((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  if (EPI == LIN_GATED) return launch(gate_up_bf16_kernel, dim3(blocks), dim3(256), 0, st, tmp, static_cast<bf16*>(act), n / 2, total);
+  if (gated)
+    return launch(gate_up_bf16_kernel, dim3(blocks), dim3(256), 0, st, tmp, static_cast<bf16*>(act), n / 2, total, EPI == LIN_GATED_CLAMP ? limit : 0.0f);
   return launch(bf16_rows_to_f32_kernel, dim3(blocks), dim3(256), 0, st, tmp, bias, out, n, total);
 }
 
 bool takes_umma(const mtx_layered* e, int rows, int n, int k) { return fits_umma(e, n, k) && rows >= 16; }
 
 template <typename T, int EPI>
-int linear(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st) {
+int linear(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st,
+           float limit = 0.0f) {
   if constexpr (sizeof(T) == 2) {
-    if (takes_umma(e, rows, n, k)) return run_linear_umma<EPI>(e, a, w, bias, out, act, rows, n, k, st);
+    if (takes_umma(e, rows, n, k)) return run_linear_umma<EPI>(e, a, w, bias, out, act, rows, n, k, st, limit);
   }
-  return run_linear<T, EPI>(e, a, w, bias, out, act, rows, n, k, st);
+  return run_linear<T, EPI>(e, a, w, bias, out, act, rows, n, k, st, limit);
+}
+
+// one matrix product per group of slots (linear_any.cuh, grouped mode): slot ranges group_off [groups + 1] on the device, at most
+// `slots` slots in all; slot s reads row a_row[s] of `a` (a_row null: row s)
+template <typename T, int EPI>
+int linear_grouped(const void* a, const int* a_row, const void* w, long long w_stride, const int* group_off, int groups, float* out, void* act,
+                   int slots, int n, int k, float limit, cudaStream_t st) {
+  if (slots <= 0) return MTX_OK;
+  LinArgs<T> p;
+  memset(&p, 0, sizeof(p));
+  p.a = static_cast<const T*>(a);
+  p.w = static_cast<const T*>(w);
+  p.out = out;
+  p.act = static_cast<T*>(act);
+  p.lda = k;
+  p.ldo = (EPI == LIN_GATED || EPI == LIN_GATED_CLAMP) ? n / 2 : n;
+  p.rows = slots;
+  p.n = n;
+  p.k = k;
+  p.limit = limit;
+  p.group_off = group_off;
+  p.a_row = a_row;
+  p.w_group_stride = w_stride;
+  const dim3 grid((n + 63) / 64, (slots + 63) / 64, groups);
+  if constexpr (sizeof(T) == 4) return launch(linear_f32_kernel<EPI>, grid, dim3(kLinF32Threads), 0, st, p);
+  else return launch(linear_mma_kernel<EPI>, grid, dim3(kLinThreads), 0, st, p);
 }
 
 int pick_key_tile(const mtx_layer_desc& l) {
@@ -268,108 +324,421 @@ bool use_window_decode() {
   return on != 0;
 }
 
+// a MTX_MIXER_WINDOW_SIGMOID layer with MTX_NORM_OUT_GAIN norms: both sublayers read x itself (xa = x in the matmul dtype)
+template <typename T>
+int window_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_t st) {
+  const mtx_layered_config& c = e->cfg;
+  const int rows = b.rows, E = c.width;
+  T* xa = static_cast<T*>(e->xa);
+  const mtx_layer_desc& l = e->layers[li];
+  const int H = l.heads, G = l.kv_heads, nq = H * l.dim, nqkv = nq + G * l.dim + G * l.vdim, no = H * l.vdim;
+  // q, k, v = W x + b
+  QkvPostArgs<T> qa;
+  memset(&qa, 0, sizeof(qa));
+  if (sizeof(T) == 2 && takes_umma(e, rows, nqkv, E)) {  // the tcgen05 GEMM's bf16 result; the bias is added where it is read
+    MTX_TRY(run_umma_raw(e, xa, l.wqkv, rows, nqkv, E, st));
+    qa.qkv_bf16 = static_cast<const bf16*>(e->obf);
+    qa.bias = l.bqkv;
+  } else {
+    if (l.bqkv) MTX_TRY((linear<T, LIN_BIAS>(e, xa, l.wqkv, l.bqkv, e->qkv, nullptr, rows, nqkv, E, st)));
+    else MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.wqkv, nullptr, e->qkv, nullptr, rows, nqkv, E, st)));
+    qa.qkv = e->qkv;
+  }
+  qa.q_norm = l.q_norm;
+  qa.k_norm = l.k_norm;
+  qa.q_out = static_cast<T*>(e->q);
+  qa.k_pages = static_cast<T*>(l.k_pages);
+  qa.v_pages = static_cast<T*>(l.v_pages);
+  qa.v_shared = e->v_shared;
+  qa.group = b.group;
+  qa.pos = b.pos;
+  qa.page_map = b.page_map;
+  qa.heads = H;
+  qa.kv_heads = G;
+  qa.dim = l.dim;
+  qa.vdim = l.vdim;
+  qa.num_pages = c.num_pages;
+  qa.tokens_per_page = c.tokens_per_page;
+  qa.max_pages = c.max_pages_per_group;
+  qa.value_mix = l.value_mix;
+  qa.value_lambda = l.value_lambda;
+  qa.eps = c.eps;
+  MTX_TRY(launch(qkv_post_kernel<T>, dim3(rows), dim3(256), 0, st, qa));
+  // the mixer
+  WindowAttnArgs<T> wa;
+  memset(&wa, 0, sizeof(wa));
+  wa.q = static_cast<const T*>(e->q);
+  wa.out = static_cast<T*>(e->attn);
+  wa.k_pages = static_cast<const T*>(l.k_pages);
+  wa.v_pages = static_cast<const T*>(l.v_pages);
+  wa.group = b.group;
+  wa.pos = b.pos;
+  wa.page_map = b.page_map;
+  wa.dist_bias = l.dist_bias;
+  wa.head_bias = l.head_bias;
+  wa.talk = l.talk;
+  wa.rows = rows;
+  wa.heads = H;
+  wa.kv_heads = G;
+  wa.dim = l.dim;
+  wa.vdim = l.vdim;
+  wa.window = l.window;
+  wa.num_pages = c.num_pages;
+  wa.tokens_per_page = c.tokens_per_page;
+  wa.max_pages = c.max_pages_per_group;
+  wa.scale = l.scale;
+  wa.softcap = l.softcap;
+  bool done = false;
+  if constexpr (sizeof(T) == 2) {
+    static const int force_stages = env_int("MTX_WINDOW_DECODE_STAGES", 0);
+    const WindowDecodePlan dplan = window_decode_plan(H, G, l.dim, l.vdim, force_stages);
+    const WindowMmaPlan plan = window_mma_plan(H, G, l.dim, l.vdim);
+    if (dplan.ok && b.n_tiles == rows && b.tile_row0 != nullptr && use_window_mma() && use_window_decode()) {  // all single-row tiles
+      MTX_TRY(launch_window_decode(e, wa, dplan, st));
+      done = true;
+    } else if (plan.ok && b.n_tiles > 0 && b.tile_row0 != nullptr && use_window_mma()) {
+      MTX_TRY(launch_window_mma(e, wa, plan, b, st));
+      done = true;
+    }
+  }
+  if (!done) {
+    wa.kt = pick_key_tile(l);
+    const size_t smem = window_attn_smem_bytes(H, G, l.dim, l.vdim, wa.kt);
+    static size_t attr_bytes[2] = {0, 0};  // per instantiation (bf16, float)
+    size_t& have = attr_bytes[sizeof(T) == 4 ? 1 : 0];
+    if (smem > 48 * 1024 && smem > have) {
+      MTX_CUDA(cudaFuncSetAttribute(window_attention_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+      have = smem;
+    }
+    MTX_TRY(launch(window_attention_rows_kernel<T>, dim3(rows), dim3(kWinThreads), smem, st, wa));
+  }
+  // x += gain1 * unit(Wo attn)
+  MTX_TRY(project_norm_residual<T>(e, e->attn, l.wo, rows, E, no, l.gain1, st));
+  if (l.ff > 0) {
+    // x += gain2 * unit(Wdown (gelu(Wgate x) * Wup x))
+    MTX_TRY((linear<T, LIN_GATED>(e, xa, l.w_gate_up, nullptr, nullptr, e->act, rows, 2 * l.ff, E, st)));
+    MTX_TRY(project_norm_residual<T>(e, e->act, l.w_down, rows, E, l.ff, l.gain2, st));
+  }
+  return MTX_OK;
+}
+
+// Column layout of a composite mixer's input projection and of the activation its output projection reads.
+struct CompositeCols {
+  int aq = 0, ak = 0, av = -1, rq = 0, rk = 0, rv = 0, rg = 0, rx = 0, n = 0;
+  int out_rec = 0, k_out = 0;
+};
+
+CompositeCols composite_cols(const mtx_layer_desc& l) {
+  CompositeCols cc;
+  int at = 0;
+  const mtx_softmax_attn_desc& a = l.attn;
+  const mtx_recurrent_desc& r = l.rec;
+  if (a.heads > 0) {
+    cc.aq = at;
+    at += a.heads * a.dim;
+    cc.ak = at;
+    at += a.kv_heads * a.dim;
+    if (!a.values_are_keys) {
+      cc.av = at;
+      at += a.kv_heads * a.vdim;
+    }
+    cc.out_rec = a.heads * a.vdim;
+  }
+  if (r.kind != 0) {
+    cc.rq = at;
+    at += r.heads * r.dim;
+    cc.rk = at;
+    at += r.heads * r.dim;
+    cc.rv = at;
+    at += r.heads * r.vdim;
+    cc.rg = at;
+    at += r.heads * r.vdim;
+    cc.rx = at;
+    at += r.kind == MTX_REC_GLA ? r.decay_rank : 2 * r.heads;
+  }
+  cc.n = at;
+  cc.k_out = cc.out_rec + (r.kind != 0 ? r.heads * r.vdim : 0);
+  return cc;
+}
+
+template <int KIND>
+int launch_rec_scan(const RecScanArgs& ra, dim3 grid, size_t smem, cudaStream_t st) {
+  const int rpt = (ra.dim + kRecSlices - 1) / kRecSlices;
+  if (rpt <= 4) return launch(recurrent_scan_kernel<KIND, 4>, grid, dim3(kRecThreads), smem, st, ra);
+  if (rpt <= 8) return launch(recurrent_scan_kernel<KIND, 8>, grid, dim3(kRecThreads), smem, st, ra);
+  if (rpt <= 16) return launch(recurrent_scan_kernel<KIND, 16>, grid, dim3(kRecThreads), smem, st, ra);
+  return launch(recurrent_scan_kernel<KIND, 32>, grid, dim3(kRecThreads), smem, st, ra);
+}
+
+// MTX_NORM_SANDWICH: x += wnorm(y + bias, post), then what comes before the next sublayer: the pre-adds of the next layer run
+// (when this was a layer's last sublayer) and xa = wnorm(x, the next sublayer's weight).  `next_layer` < 0: the next sublayer is
+// this layer's feed-forward, whose weight is `pre`.
+template <typename T>
+int sandwich_step(mtx_layered* e, const float* y, const float* bias, const float* post, const float* pre, int next_layer, int rows, cudaStream_t st) {
+  SandwichArgs sa;
+  memset(&sa, 0, sizeof(sa));
+  sa.y = y;
+  sa.y_bias = bias;
+  sa.post = post;
+  sa.pre = pre;
+  sa.x = e->x;
+  sa.eps = e->cfg.eps;
+  sa.width = e->cfg.width;
+  if (next_layer >= 0 && next_layer < e->cfg.num_layers) {
+    const mtx_layer_desc& nl = e->layers[next_layer];
+    sa.x0 = nl.add_embedding ? e->x0 : nullptr;
+    sa.add_vec = nl.add_vector;
+    sa.pre = nl.norm1;
+  }
+  if (!sa.y && !sa.x0 && !sa.add_vec && !sa.pre) return MTX_OK;
+  return launch(sandwich_step_kernel<T>, dim3(rows), dim3(256), 0, st, sa, static_cast<T*>(e->xa));
+}
+
+// a MTX_MIXER_COMPOSITE layer with MTX_NORM_SANDWICH norms; xa holds wnorm(x, norm1) on entry
+template <typename T>
+int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_t st) {
+  const mtx_layered_config& c = e->cfg;
+  const mtx_layer_desc& l = e->layers[li];
+  const int rows = b.rows, E = c.width;
+  T* xa = static_cast<T*>(e->xa);
+  const CompositeCols cc = composite_cols(l);
+  const int n_in = l.n_in;
+  if (l.b_in) MTX_TRY((linear<T, LIN_BIAS>(e, xa, l.w_in, l.b_in, e->qkv, nullptr, rows, n_in, E, st)));
+  else MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.w_in, nullptr, e->qkv, nullptr, rows, n_in, E, st)));
+  T* mix = static_cast<T*>(e->attn);  // [rows, k_out]: the attention's heads, then the recurrence's
+  if (l.attn.heads > 0) {
+    const mtx_softmax_attn_desc& a = l.attn;
+    RopeAppendArgs<T> ra;
+    memset(&ra, 0, sizeof(ra));
+    ra.proj = e->qkv;
+    ra.ld = n_in;
+    ra.q_col = cc.aq;
+    ra.k_col = cc.ak;
+    ra.v_col = cc.av;
+    ra.rot_freq = a.rot_freq;
+    ra.q_out = static_cast<T*>(e->q);
+    ra.k_pages = static_cast<T*>(a.k_pages);
+    ra.v_pages = static_cast<T*>(a.v_pages);
+    ra.group = b.group;
+    ra.pos = b.pos;
+    ra.page_map = b.page_map;
+    ra.heads = a.heads;
+    ra.kv_heads = a.kv_heads;
+    ra.dim = a.dim;
+    ra.vdim = a.vdim;
+    ra.rot_dims = a.rot_dims;
+    ra.num_pages = c.num_pages;
+    ra.tokens_per_page = c.tokens_per_page;
+    ra.max_pages = c.max_pages_per_group;
+    MTX_TRY(launch(rope_append_kernel<T>, dim3(rows), dim3(256), 0, st, ra));
+    SoftmaxAttnArgs<T> sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.q = static_cast<const T*>(e->q);
+    sa.out = mix;
+    sa.ld_out = cc.k_out;
+    sa.k_pages = static_cast<const T*>(a.k_pages);
+    sa.v_pages = static_cast<const T*>(a.v_pages);
+    sa.group = b.group;
+    sa.pos = b.pos;
+    sa.page_map = b.page_map;
+    sa.tile_row0 = b.tile_row0;
+    sa.heads = a.heads;
+    sa.kv_heads = a.kv_heads;
+    sa.dim = a.dim;
+    sa.vdim = a.vdim;
+    sa.window = a.window;
+    sa.num_pages = c.num_pages;
+    sa.tokens_per_page = c.tokens_per_page;
+    sa.max_pages = c.max_pages_per_group;
+    sa.scale = a.scale;
+    sa.out_scale = a.out_scale;
+    const size_t smem = softmax_attn_smem_bytes(a.dim, a.vdim);
+    static size_t attr_bytes[2] = {0, 0};  // per instantiation (bf16, float)
+    size_t& have = attr_bytes[sizeof(T) == 4 ? 1 : 0];
+    if (smem > 48 * 1024 && smem > have) {
+      MTX_CUDA(cudaFuncSetAttribute(softmax_attention_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+      have = smem;
+    }
+    MTX_TRY(launch(softmax_attention_rows_kernel<T>, dim3(b.n_tiles, a.heads), dim3(kSmaxThreads), smem, st, sa));
+  }
+  if (l.rec.kind != 0) {
+    const mtx_recurrent_desc& r = l.rec;
+    RecPrepareArgs pa;
+    memset(&pa, 0, sizeof(pa));
+    pa.proj = e->qkv;
+    pa.ld = n_in;
+    pa.x_col = cc.rx;
+    pa.kind = r.kind;
+    pa.heads = r.heads;
+    pa.dim = r.dim;
+    pa.rank = r.decay_rank;
+    pa.tau = r.tau;
+    pa.cap = r.gate_cap;
+    pa.up_t = r.decay_up_t;
+    pa.bias = r.kind == MTX_REC_GLA ? r.decay_bias : r.gate_bias;
+    pa.out = e->rec_aux;
+    MTX_TRY(launch(recurrent_prepare_kernel, dim3(rows), dim3(256), r.kind == MTX_REC_GLA ? sizeof(float) * r.decay_rank : 0, st, pa));
+    RecScanArgs ra;
+    memset(&ra, 0, sizeof(ra));
+    ra.proj = e->qkv;
+    ra.ld = n_in;
+    ra.q_col = cc.rq;
+    ra.k_col = cc.rk;
+    ra.v_col = cc.rv;
+    ra.aux = e->rec_aux;
+    ra.o = e->rec_o;
+    ra.state_s = r.state_s;
+    ra.state_n = r.state_n;
+    ra.state_m = r.state_m;
+    ra.run_row0 = b.run_row0;
+    ra.group = b.group;
+    ra.pos = b.pos;
+    ra.heads = r.heads;
+    ra.dim = r.dim;
+    ra.vdim = r.vdim;
+    ra.chunk = rec_chunk_tokens(r.dim);
+    ra.q_scale = r.q_scale;
+    ra.denom_eps = r.denom_eps;
+    const dim3 grid(b.n_runs, r.heads, (r.vdim + kRecCols - 1) / kRecCols);
+    const size_t smem = rec_scan_smem_bytes(r.dim, ra.chunk);
+    if (r.kind == MTX_REC_GLA) MTX_TRY(launch_rec_scan<REC_GLA>(ra, grid, smem, st));
+    else MTX_TRY(launch_rec_scan<REC_MLSTM>(ra, grid, smem, st));
+    RecOutArgs<T> oa;
+    memset(&oa, 0, sizeof(oa));
+    oa.o = e->rec_o;
+    oa.proj = e->qkv;
+    oa.ld = n_in;
+    oa.g_col = cc.rg;
+    oa.weight = r.out_norm;
+    oa.out = mix;
+    oa.ld_out = cc.k_out;
+    oa.out_col = cc.out_rec;
+    oa.heads = r.heads;
+    oa.vdim = r.vdim;
+    oa.gate_silu = r.gate_silu;
+    oa.eps = c.eps;
+    oa.out_scale = r.out_scale;
+    MTX_TRY(launch(recurrent_out_kernel<T>, dim3(rows), dim3(256), 0, st, oa));
+  }
+  MTX_TRY((linear<T, LIN_PLAIN>(e, mix, l.wo, nullptr, e->y, nullptr, rows, E, cc.k_out, st)));
+  const bool has_ff = l.ff_kind == MTX_FF_MOE ? l.moe.experts > 0 : l.ff > 0;
+  MTX_TRY(sandwich_step<T>(e, e->y, l.bo, l.norm1b, has_ff ? l.norm2 : nullptr, has_ff ? -1 : li + 1, rows, st));
+  if (!has_ff) return MTX_OK;
+  if (l.ff_kind == MTX_FF_MOE) {
+    const mtx_moe_desc& m = l.moe;
+    const int entries = rows * m.top;
+    MTX_TRY((linear<T, LIN_PLAIN>(e, xa, m.w_router, nullptr, e->moe_logits, nullptr, rows, m.experts, E, st)));
+    MoeRouteArgs ra;
+    memset(&ra, 0, sizeof(ra));
+    ra.logits = e->moe_logits;
+    ra.correction = m.correction;
+    ra.chosen = e->moe_chosen;
+    ra.weight = e->moe_weight;
+    ra.experts = m.experts;
+    ra.top = m.top;
+    ra.groups = m.groups;
+    ra.keep = m.keep_groups;
+    MTX_TRY(launch(moe_route_kernel, dim3(rows), dim3(32), sizeof(float) * (2 * m.experts + m.groups), st, ra));
+    MTX_TRY(launch(moe_sort_kernel, dim3(1), dim3(1024), sizeof(int) * (2 * m.experts + 1), st, (const int*)e->moe_chosen, entries, m.top, m.experts,
+                   e->moe_off, e->moe_slot, e->moe_row));
+    MTX_TRY((linear_grouped<T, LIN_GATED_CLAMP>(xa, e->moe_row, m.w_gate_up, (long long)2 * m.ff * E, e->moe_off, m.experts, nullptr, e->moe_act, entries,
+                                                2 * m.ff, E, m.limit, st)));
+    MTX_TRY((linear_grouped<T, LIN_PLAIN>(e->moe_act, nullptr, m.w_down, (long long)E * m.ff, e->moe_off, m.experts, e->moe_y, nullptr, entries, E, m.ff,
+                                          0.0f, st)));
+    if (m.shared_ff > 0) {
+      MTX_TRY((linear<T, LIN_GATED_CLAMP>(e, xa, m.shared_gate_up, nullptr, nullptr, e->act, rows, 2 * m.shared_ff, E, st, m.shared_limit)));
+      MTX_TRY((linear<T, LIN_PLAIN>(e, e->act, m.shared_down, nullptr, e->y, nullptr, rows, E, m.shared_ff, st)));
+    }
+    MTX_TRY(launch(moe_combine_kernel, dim3(rows), dim3(256), 0, st, (const float*)e->moe_y, (const int*)e->moe_slot, (const float*)e->moe_weight, m.top, E,
+                   m.shared_ff > 0 ? 1 : 0, e->y));
+  } else {
+    if (l.ff_kind == MTX_FF_CLAMPED_GATED)
+      MTX_TRY((linear<T, LIN_GATED_CLAMP>(e, xa, l.w_gate_up, nullptr, nullptr, e->act, rows, 2 * l.ff, E, st, l.ff_limit)));
+    else MTX_TRY((linear<T, LIN_GATED>(e, xa, l.w_gate_up, nullptr, nullptr, e->act, rows, 2 * l.ff, E, st)));
+    MTX_TRY((linear<T, LIN_PLAIN>(e, e->act, l.w_down, nullptr, e->y, nullptr, rows, E, l.ff, st)));
+  }
+  return sandwich_step<T>(e, e->y, nullptr, l.norm2b, nullptr, li + 1, rows, st);
+}
+
 template <typename T>
 int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
   const mtx_layered_config& c = e->cfg;
   const int rows = b.rows, E = c.width;
   T* xa = static_cast<T*>(e->xa);
-  MTX_TRY(launch(embed_rows_kernel<T>, dim3(rows), dim3(128), 0, st, b.token, static_cast<const T*>(c.embedding), c.vocab, c.embed_scale, e->x, xa, E));
+  MTX_TRY(launch(embed_rows_kernel<T>, dim3(rows), dim3(128), 0, st, b.token, static_cast<const T*>(c.embedding), c.vocab, c.embed_scale, e->x, xa, E,
+                 e->sandwich ? e->x0 : (float*)nullptr));
+  if (e->sandwich) MTX_TRY(sandwich_step<T>(e, nullptr, nullptr, nullptr, nullptr, 0, rows, st));  // layer 0's pre-adds and pre-norm
   for (int li = 0; li < c.num_layers; ++li) {
-    const mtx_layer_desc& l = e->layers[li];
-    const int H = l.heads, G = l.kv_heads, nq = H * l.dim, nqkv = nq + G * l.dim + G * l.vdim, no = H * l.vdim;
-    // q, k, v = W x + b
-    QkvPostArgs<T> qa;
-    memset(&qa, 0, sizeof(qa));
-    if (sizeof(T) == 2 && takes_umma(e, rows, nqkv, E)) {  // the tcgen05 GEMM's bf16 result; the bias is added where it is read
-      MTX_TRY(run_umma_raw(e, xa, l.wqkv, rows, nqkv, E, st));
-      qa.qkv_bf16 = static_cast<const bf16*>(e->obf);
-      qa.bias = l.bqkv;
-    } else {
-      if (l.bqkv) MTX_TRY((linear<T, LIN_BIAS>(e, xa, l.wqkv, l.bqkv, e->qkv, nullptr, rows, nqkv, E, st)));
-      else MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.wqkv, nullptr, e->qkv, nullptr, rows, nqkv, E, st)));
-      qa.qkv = e->qkv;
-    }
-    qa.q_norm = l.q_norm;
-    qa.k_norm = l.k_norm;
-    qa.q_out = static_cast<T*>(e->q);
-    qa.k_pages = static_cast<T*>(l.k_pages);
-    qa.v_pages = static_cast<T*>(l.v_pages);
-    qa.v_shared = e->v_shared;
-    qa.group = b.group;
-    qa.pos = b.pos;
-    qa.page_map = b.page_map;
-    qa.heads = H;
-    qa.kv_heads = G;
-    qa.dim = l.dim;
-    qa.vdim = l.vdim;
-    qa.num_pages = c.num_pages;
-    qa.tokens_per_page = c.tokens_per_page;
-    qa.max_pages = c.max_pages_per_group;
-    qa.value_mix = l.value_mix;
-    qa.value_lambda = l.value_lambda;
-    qa.eps = c.eps;
-    MTX_TRY(launch(qkv_post_kernel<T>, dim3(rows), dim3(256), 0, st, qa));
-    // the mixer
-    WindowAttnArgs<T> wa;
-    memset(&wa, 0, sizeof(wa));
-    wa.q = static_cast<const T*>(e->q);
-    wa.out = static_cast<T*>(e->attn);
-    wa.k_pages = static_cast<const T*>(l.k_pages);
-    wa.v_pages = static_cast<const T*>(l.v_pages);
-    wa.group = b.group;
-    wa.pos = b.pos;
-    wa.page_map = b.page_map;
-    wa.dist_bias = l.dist_bias;
-    wa.head_bias = l.head_bias;
-    wa.talk = l.talk;
-    wa.rows = rows;
-    wa.heads = H;
-    wa.kv_heads = G;
-    wa.dim = l.dim;
-    wa.vdim = l.vdim;
-    wa.window = l.window;
-    wa.num_pages = c.num_pages;
-    wa.tokens_per_page = c.tokens_per_page;
-    wa.max_pages = c.max_pages_per_group;
-    wa.scale = l.scale;
-    wa.softcap = l.softcap;
-    bool done = false;
-    if constexpr (sizeof(T) == 2) {
-      static const int force_stages = env_int("MTX_WINDOW_DECODE_STAGES", 0);
-      const WindowDecodePlan dplan = window_decode_plan(H, G, l.dim, l.vdim, force_stages);
-      const WindowMmaPlan plan = window_mma_plan(H, G, l.dim, l.vdim);
-      if (dplan.ok && b.n_tiles == rows && b.tile_row0 != nullptr && use_window_mma() && use_window_decode()) {  // all single-row tiles
-        MTX_TRY(launch_window_decode(e, wa, dplan, st));
-        done = true;
-      } else if (plan.ok && b.n_tiles > 0 && b.tile_row0 != nullptr && use_window_mma()) {
-        MTX_TRY(launch_window_mma(e, wa, plan, b, st));
-        done = true;
-      }
-    }
-    if (!done) {
-      wa.kt = pick_key_tile(l);
-      const size_t smem = window_attn_smem_bytes(H, G, l.dim, l.vdim, wa.kt);
-      static size_t attr_bytes[2] = {0, 0};  // per instantiation (bf16, float)
-      size_t& have = attr_bytes[sizeof(T) == 4 ? 1 : 0];
-      if (smem > 48 * 1024 && smem > have) {
-        MTX_CUDA(cudaFuncSetAttribute(window_attention_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        have = smem;
-      }
-      MTX_TRY(launch(window_attention_rows_kernel<T>, dim3(rows), dim3(kWinThreads), smem, st, wa));
-    }
-    // x += gain1 * unit(Wo attn)
-    MTX_TRY(project_norm_residual<T>(e, e->attn, l.wo, rows, E, no, l.gain1, st));
-    if (l.ff > 0) {
-      // x += gain2 * unit(Wdown (gelu(Wgate x) * Wup x))
-      MTX_TRY((linear<T, LIN_GATED>(e, xa, l.w_gate_up, nullptr, nullptr, e->act, rows, 2 * l.ff, E, st)));
-      MTX_TRY(project_norm_residual<T>(e, e->act, l.w_down, rows, E, l.ff, l.gain2, st));
-    }
+    if (e->layers[li].mixer == MTX_MIXER_COMPOSITE) MTX_TRY(composite_layer<T>(e, li, b, st));
+    else MTX_TRY(window_layer<T>(e, li, b, st));
   }
   if (b.n_want > 0) {
     T* wn = static_cast<T*>(e->wanted);
-    MTX_TRY(launch(scalar_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_gain, c.eps, wn, E));
+    if (c.final_norm) MTX_TRY(launch(weighted_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_norm, c.eps, wn, E));
+    else MTX_TRY(launch(scalar_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_gain, c.eps, wn, E));
     MTX_TRY((linear<T, LIN_PLAIN>(e, wn, c.head, nullptr, b.logits, nullptr, b.n_want, c.vocab, E, st)));
+    if (c.logit_softcap > 0.0f) {
+      const long long total = (long long)b.n_want * c.vocab;
+      const int blocks = int((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+      MTX_TRY(launch(softcap_kernel, dim3(blocks), dim3(256), 0, st, b.logits, c.logit_softcap, total));
+    }
   }
+  return MTX_OK;
+}
+
+// validation and workspace sizes of a MTX_MIXER_COMPOSITE layer
+int check_composite(mtx_layered* e, int i) {
+  const mtx_layer_desc& l = e->layers[i];
+  const mtx_softmax_attn_desc& a = l.attn;
+  const mtx_recurrent_desc& r = l.rec;
+  if (l.norm_style != MTX_NORM_SANDWICH) return fail(MTX_ERR_UNSUPPORTED, "layer %d: a composite mixer layer has sandwich norms", i);
+  if (!l.norm1 || !l.norm1b || !l.w_in || !l.wo) return fail(MTX_ERR_ARG, "layer %d: a norm weight or a projection is missing", i);
+  if (a.heads <= 0 && r.kind == 0) return fail(MTX_ERR_ARG, "layer %d: a composite mixer needs an attention or a recurrence", i);
+  if (a.heads > 0) {
+    if (a.kv_heads < 1 || a.heads % a.kv_heads != 0 || a.dim < 1 || a.vdim < 1 || a.window < 0) return fail(MTX_ERR_ARG, "layer %d: bad attention geometry", i);
+    if (a.values_are_keys && a.vdim != a.dim) return fail(MTX_ERR_ARG, "layer %d: values that are the keys need vdim == dim", i);
+    if (a.rot_dims < 0 || a.rot_dims > a.dim || (a.rot_dims & 1) || (a.rot_dims > 0 && !a.rot_freq)) return fail(MTX_ERR_ARG, "layer %d: bad rot_dims / rot_freq", i);
+    if (!a.k_pages || !a.v_pages) return fail(MTX_ERR_ARG, "layer %d: a page pool is missing", i);
+    if (kSmaxRows * a.vdim > kSmaxThreads * kSmaxMaxAcc) return fail(MTX_ERR_UNSUPPORTED, "layer %d: vdim %d exceeds %d", i, a.vdim, kSmaxThreads * kSmaxMaxAcc / kSmaxRows);
+    if (softmax_attn_smem_bytes(a.dim, a.vdim) > 200 * 1024) return fail(MTX_ERR_UNSUPPORTED, "layer %d: the attention's heads do not fit shared memory", i);
+    if (a.heads * a.dim > e->max_qdim) e->max_qdim = a.heads * a.dim;
+  }
+  if (r.kind != 0) {
+    if (r.kind != MTX_REC_GLA && r.kind != MTX_REC_MLSTM) return fail(MTX_ERR_UNSUPPORTED, "layer %d: unknown recurrence %d", i, r.kind);
+    if (r.heads < 1 || r.dim < 1 || r.vdim < 1 || r.dim > kRecSlices * 32) return fail(MTX_ERR_UNSUPPORTED, "layer %d: recurrence heads / dim (<= %d) / vdim", i, kRecSlices * 32);
+    if (!r.state_s || !r.out_norm) return fail(MTX_ERR_ARG, "layer %d: the recurrence's state or output norm is missing", i);
+    if (r.kind == MTX_REC_GLA && (r.decay_rank < 1 || !r.decay_up_t || !(r.tau > 0.0f))) return fail(MTX_ERR_ARG, "layer %d: the decay's projection / tau is missing", i);
+    if (r.kind == MTX_REC_MLSTM && (!r.state_n || !r.state_m || !r.gate_bias || !(r.gate_cap > 0.0f))) return fail(MTX_ERR_ARG, "layer %d: mLSTM state / gate bias / cap missing", i);
+    if (r.heads * r.vdim > e->max_rec_o) e->max_rec_o = r.heads * r.vdim;
+    const int aux = r.kind == MTX_REC_GLA ? r.heads * r.dim : 2 * r.heads;
+    if (aux > e->max_rec_aux) e->max_rec_aux = aux;
+  }
+  const CompositeCols cc = composite_cols(l);
+  if (l.n_in < cc.n) return fail(MTX_ERR_ARG, "layer %d: n_in = %d, the sub-mixers need %d projection rows", i, l.n_in, cc.n);
+  if (l.n_in > e->max_nqkv) e->max_nqkv = l.n_in;
+  if (cc.k_out > e->max_odim) e->max_odim = cc.k_out;
+  if (l.ff_kind == MTX_FF_MOE) {
+    const mtx_moe_desc& m = l.moe;
+    if (m.experts > 0) {
+      if (!l.norm2 || !l.norm2b) return fail(MTX_ERR_ARG, "layer %d: a feed-forward norm weight is missing", i);
+      if (m.top < 1 || m.top > m.experts || m.groups < 1 || m.experts % m.groups != 0 || m.keep_groups < 1 || m.keep_groups > m.groups || m.ff < 1)
+        return fail(MTX_ERR_ARG, "layer %d: bad expert / top / groups / ff", i);
+      if (m.keep_groups * (m.experts / m.groups) < m.top) return fail(MTX_ERR_ARG, "layer %d: the kept groups hold fewer than `top` experts", i);
+      if (m.experts > 4096) return fail(MTX_ERR_UNSUPPORTED, "layer %d: more than 4096 experts", i);
+      if (!m.w_router || !m.w_gate_up || !m.w_down || (m.shared_ff > 0 && (!m.shared_gate_up || !m.shared_down))) return fail(MTX_ERR_ARG, "layer %d: an expert weight is missing", i);
+      if (m.top > e->max_moe_top) e->max_moe_top = m.top;
+      if (m.experts > e->max_moe_experts) e->max_moe_experts = m.experts;
+      if (m.ff > e->max_moe_ff) e->max_moe_ff = m.ff;
+      if (m.shared_ff > e->max_ff) e->max_ff = m.shared_ff;
+      if (2 * m.shared_ff > e->max_nqkv) e->max_nqkv = 2 * m.shared_ff;
+    }
+  } else if (l.ff > 0) {
+    if (!l.norm2 || !l.norm2b || !l.w_gate_up || !l.w_down) return fail(MTX_ERR_ARG, "layer %d: a feed-forward weight is missing", i);
+    if (l.ff_kind != MTX_FF_GELU_GATED && l.ff_kind != MTX_FF_CLAMPED_GATED) return fail(MTX_ERR_UNSUPPORTED, "layer %d: unknown feed-forward kind %d", i, l.ff_kind);
+    if (2 * l.ff > e->max_nqkv) e->max_nqkv = 2 * l.ff;
+    if (l.ff > e->max_ff) e->max_ff = l.ff;
+  }
+  e->sandwich = true;
   return MTX_OK;
 }
 
@@ -390,7 +759,17 @@ int mtx_layered_create(const mtx_layered_config* cfg, const mtx_layer_desc* laye
   for (int i = 0; i < c.num_layers; ++i) {
     const mtx_layer_desc& l = e->layers[i];
     int rc = MTX_OK;
+    if (l.mixer == MTX_MIXER_COMPOSITE) {
+      rc = check_composite(e, i);
+      if (rc != MTX_OK) {
+        delete e;
+        return rc;
+      }
+      continue;
+    }
     if (l.mixer != MTX_MIXER_WINDOW_SIGMOID) rc = fail(MTX_ERR_UNSUPPORTED, "layer %d: unknown mixer %d", i, l.mixer);
+    else if (l.norm_style != MTX_NORM_OUT_GAIN || l.ff_kind != MTX_FF_GELU_GATED)
+      rc = fail(MTX_ERR_UNSUPPORTED, "layer %d: a window mixer layer has output-gain norms and a gelu-gated feed-forward", i);
     else if (l.heads < 1 || l.kv_heads < 1 || l.heads % l.kv_heads != 0 || l.dim < 1 || l.vdim < 1 || l.window < 1 || l.ff < 0)
       rc = fail(MTX_ERR_ARG, "layer %d: bad head geometry / window / ff", i);
     else if (l.heads * l.vdim > kWinThreads * kWinMaxAcc)
@@ -417,6 +796,15 @@ int mtx_layered_create(const mtx_layered_config* cfg, const mtx_layer_desc* laye
     if (l.heads * l.vdim > e->max_odim) e->max_odim = l.heads * l.vdim;
     if (2 * l.ff > e->max_nqkv) e->max_nqkv = 2 * l.ff;  // (the tcgen05 path parks the gate / up product in the same scratch)
     if (l.ff > e->max_ff) e->max_ff = l.ff;
+  }
+  for (int i = 0; i < c.num_layers; ++i)
+    if ((e->layers[i].norm_style == MTX_NORM_SANDWICH) != e->sandwich) {
+      delete e;
+      return fail(MTX_ERR_UNSUPPORTED, "layer %d: all layers of a model share one norm style", i);
+    }
+  if (e->sandwich && c.width > 256 * kSandwichMax) {
+    delete e;
+    return fail(MTX_ERR_UNSUPPORTED, "width %d exceeds %d", c.width, 256 * kSandwichMax);
   }
   if (c.vocab > e->max_nqkv) e->max_nqkv = c.vocab;
   int dev = 0, sms = 0;
@@ -455,6 +843,17 @@ int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes) {
   e->obf = base + L.obf;
   e->attn_part = reinterpret_cast<float*>(base + L.attn_part);
   e->attn_part_rows = 4 * align_up(size_t(e->cfg.max_rows), 256);
+  e->x0 = reinterpret_cast<float*>(base + L.x0);
+  e->rec_o = reinterpret_cast<float*>(base + L.rec_o);
+  e->rec_aux = reinterpret_cast<float*>(base + L.rec_aux);
+  e->moe_logits = reinterpret_cast<float*>(base + L.moe_logits);
+  e->moe_weight = reinterpret_cast<float*>(base + L.moe_weight);
+  e->moe_y = reinterpret_cast<float*>(base + L.moe_y);
+  e->moe_chosen = reinterpret_cast<int*>(base + L.moe_chosen);
+  e->moe_slot = reinterpret_cast<int*>(base + L.moe_slot);
+  e->moe_row = reinterpret_cast<int*>(base + L.moe_row);
+  e->moe_off = reinterpret_cast<int*>(base + L.moe_off);
+  e->moe_act = base + L.moe_act;
   e->bound = true;
   return MTX_OK;
 }
@@ -465,6 +864,8 @@ int mtx_layered_step(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream strea
   if (b->n_want < 0 || b->n_want > e->cfg.max_want) return fail(MTX_ERR_ARG, "n_want = %d outside [0, %d]", b->n_want, e->cfg.max_want);
   if (!b->token || !b->group || !b->pos || !b->page_map || (b->n_want > 0 && (!b->want_rows || !b->logits))) return fail(MTX_ERR_ARG, "null batch array");
   if (b->n_tiles < 0 || b->n_tiles > b->rows) return fail(MTX_ERR_ARG, "n_tiles = %d for %d rows", b->n_tiles, b->rows);
+  if (e->sandwich && (b->n_tiles < 1 || !b->tile_row0 || b->n_runs < 1 || b->n_runs > b->rows || !b->run_row0))
+    return fail(MTX_ERR_ARG, "this model needs the batch's query tiles and runs");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return e->cfg.float32 ? step_typed<float>(e, *b, st) : step_typed<bf16>(e, *b, st);
 }

@@ -10,13 +10,18 @@
 // Epilogues: LIN_PLAIN  out = acc                      (fp32)
 //            LIN_BIAS   out = acc + bias[col]          (fp32)
 //            LIN_GATED  act[r, f] = gelu_tanh(acc[r, 2f]) * acc[r, 2f + 1]   (the weight rows are interleaved gate / up)
+//            LIN_GATED_CLAMP  act[r, f] = g sigmoid(1.702 g) (u + 1), g = min(acc[r, 2f], limit), u = clamp(acc[r, 2f + 1], -limit, limit)
+//
+// Grouped mode (group_off != null; a mixture of experts): blockIdx.z names a group with its own weight matrix; the group's rows are
+// the slots [group_off[g], group_off[g + 1]); slot s reads row a_row[s] of `a` (or row s when a_row is null) and writes row s of the
+// output.  CTAs beyond a group's last row tile leave at once, so the grid is sized for the worst case without a host round trip.
 #pragma once
 
 #include "common.cuh"
 
 namespace mtx {
 
-enum { LIN_PLAIN = 0, LIN_BIAS = 1, LIN_GATED = 2 };
+enum { LIN_PLAIN = 0, LIN_BIAS = 1, LIN_GATED = 2, LIN_GATED_CLAMP = 3 };
 
 template <typename T>
 struct LinArgs {
@@ -27,7 +32,32 @@ struct LinArgs {
   T* act;             // [rows, n / 2], row pitch ldo (LIN_GATED)
   long long lda, ldo;
   int rows, n, k;
+  float limit;             // LIN_GATED_CLAMP
+  const int* group_off;    // grouped mode: [groups + 1] slot ranges
+  const int* a_row;        // grouped mode: [slots] row of `a` per slot, or null
+  long long w_group_stride;  // grouped mode: elements between two groups' weights
 };
+
+// grouped mode: the argument block of this CTA's group (false: the CTA has no rows)
+template <typename T>
+__device__ __forceinline__ bool lin_enter_group(LinArgs<T>& p, int tile_rows) {
+  if (p.group_off == nullptr) return true;
+  const int g = blockIdx.z, s0 = p.group_off[g], cnt = p.group_off[g + 1] - s0;
+  if (int(blockIdx.y) * tile_rows >= cnt) return false;
+  p.rows = cnt;
+  p.w += size_t(g) * p.w_group_stride;
+  if (p.a_row) p.a_row += s0;
+  else p.a += size_t(s0) * p.lda;
+  if (p.out) p.out += size_t(s0) * p.ldo;
+  if (p.act) p.act += size_t(s0) * p.ldo;
+  return true;
+}
+
+__device__ __forceinline__ float clamped_gate_f(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
 
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   const float c = 0.7978845608028654f;  // sqrt(2 / pi)
@@ -52,6 +82,10 @@ __device__ __forceinline__ void lin_store_pair(const LinArgs<T>& p, int r, int c
     p.act[size_t(r) * p.ldo + (c >> 1)] = to_act<T>(gelu_tanh_f(v0) * v1);
     return;
   }
+  if (EPI == LIN_GATED_CLAMP) {
+    p.act[size_t(r) * p.ldo + (c >> 1)] = to_act<T>(clamped_gate_f(v0, v1, p.limit));
+    return;
+  }
   float* o = p.out + size_t(r) * p.ldo + c;
   if (EPI == LIN_BIAS) {
     v0 += p.bias[c];
@@ -65,7 +99,8 @@ __device__ __forceinline__ void lin_store_pair(const LinArgs<T>& p, int r, int c
 constexpr int kLinThreads = 128;
 constexpr int kLinBM = 64, kLinBN = 64, kLinBK = 32, kLinPitch = kLinBK + 8;  // 80-byte rows: fragment reads hit 32 banks
 
-__device__ __forceinline__ void lin_load_tile(const bf16* src, long long ld, int row0, int n_rows, int k0, int k, bool vec, bf16* dst, int tid) {
+__device__ __forceinline__ void lin_load_tile(const bf16* src, long long ld, int row0, int n_rows, int k0, int k, bool vec, bf16* dst, int tid,
+                                              const int* row_map = nullptr) {
   // 64 rows x 32 columns: 256 chunks of 8 elements, two per thread
 #pragma unroll
   for (int it = 0; it < 2; ++it) {
@@ -73,7 +108,7 @@ __device__ __forceinline__ void lin_load_tile(const bf16* src, long long ld, int
     const int gr = row0 + r, gc = k0 + c;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (gr < n_rows) {
-      const bf16* s = src + size_t(gr) * ld + gc;
+      const bf16* s = src + size_t(row_map ? row_map[gr] : gr) * ld + gc;
       if (vec && gc + 8 <= k) {
         v = *reinterpret_cast<const uint4*>(s);
       } else {
@@ -88,11 +123,13 @@ __device__ __forceinline__ void lin_load_tile(const bf16* src, long long ld, int
 }
 
 template <int EPI>
-__global__ void __launch_bounds__(kLinThreads) linear_mma_kernel(const LinArgs<bf16> p) {
+__global__ void __launch_bounds__(kLinThreads) linear_mma_kernel(const LinArgs<bf16> p_in) {
   __shared__ __align__(16) bf16 sa[kLinBM * kLinPitch];
   __shared__ __align__(16) bf16 sb[kLinBN * kLinPitch];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   griddep_wait();
+  LinArgs<bf16> p = p_in;
+  if (!lin_enter_group(p, kLinBM)) return;
   const int row0 = blockIdx.y * kLinBM, col0 = blockIdx.x * kLinBN;
   const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
   const bool vec_a = (p.lda % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0);
@@ -105,7 +142,7 @@ __global__ void __launch_bounds__(kLinThreads) linear_mma_kernel(const LinArgs<b
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
   for (int k0 = 0; k0 < p.k; k0 += kLinBK) {
-    lin_load_tile(p.a, p.lda, row0, p.rows, k0, p.k, vec_a, sa, tid);
+    lin_load_tile(p.a, p.lda, row0, p.rows, k0, p.k, vec_a, sa, tid, p.a_row);
     lin_load_tile(p.w, p.k, col0, p.n, k0, p.k, vec_w, sb, tid);
     __syncthreads();
 #pragma unroll
@@ -149,11 +186,13 @@ __global__ void __launch_bounds__(kLinThreads) linear_mma_kernel(const LinArgs<b
 constexpr int kLinF32Threads = 256;
 
 template <int EPI>
-__global__ void __launch_bounds__(kLinF32Threads) linear_f32_kernel(const LinArgs<float> p) {
+__global__ void __launch_bounds__(kLinF32Threads) linear_f32_kernel(const LinArgs<float> p_in) {
   __shared__ float sa[16][64 + 4];  // [k][row]
   __shared__ float sb[16][64 + 4];  // [k][col]
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   griddep_wait();
+  LinArgs<float> p = p_in;
+  if (!lin_enter_group(p, 64)) return;
   const int row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
   float acc[4][4];
 #pragma unroll
@@ -165,7 +204,7 @@ __global__ void __launch_bounds__(kLinF32Threads) linear_f32_kernel(const LinArg
     for (int it = 0; it < 4; ++it) {  // 64 x 16 elements of each operand, four per thread; consecutive threads walk k
       const int idx = tid + it * kLinF32Threads, r = idx >> 4, c = idx & 15;
       const int gk = k0 + c;
-      sa[c][r] = (row0 + r < p.rows && gk < p.k) ? p.a[size_t(row0 + r) * p.lda + gk] : 0.0f;
+      sa[c][r] = (row0 + r < p.rows && gk < p.k) ? p.a[size_t(p.a_row ? p.a_row[row0 + r] : row0 + r) * p.lda + gk] : 0.0f;
       sb[c][r] = (col0 + r < p.n && gk < p.k) ? p.w[size_t(col0 + r) * p.k + gk] : 0.0f;
     }
     __syncthreads();

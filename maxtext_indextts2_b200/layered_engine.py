@@ -27,8 +27,18 @@ from . import page_manager
 from . import params as params_lib
 from .maxengine import ExistingPrefix, MaxEngine, ResultTokens  # noqa: F401  (same result types)
 
-_MIXERS = {"window_sigmoid": _lib.MIXER_WINDOW_SIGMOID}
-QUERY_TILE_ROWS = 16  # rows of one query tile of the tensor-core mixer (csrc/window_attention_mma.cuh)
+_MIXERS = {"window_sigmoid": _lib.MIXER_WINDOW_SIGMOID, "composite": _lib.MIXER_COMPOSITE}
+_NORMS = {"out_gain": _lib.NORM_OUT_GAIN, "sandwich": _lib.NORM_SANDWICH}
+_FF_KINDS = {"none": _lib.FF_GELU_GATED, "gelu": _lib.FF_GELU_GATED, "clamped": _lib.FF_CLAMPED_GATED, "moe": _lib.FF_MOE}
+_RECURRENCES = {"gla": _lib.REC_GLA, "mlstm": _lib.REC_MLSTM}
+QUERY_TILE_ROWS = 16  # rows of one query tile of the attention kernels (csrc/window_attention_mma.cuh, csrc/softmax_attention.cuh)
+
+_LAYER_MATS = ("wqkv", "wo", "w_gate_up", "w_down", "w_in")
+_LAYER_VECS = ("bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk", "norm1", "norm1b", "norm2", "norm2b", "add_vector", "b_in", "bo")
+_ATTN_VECS = ("rot_freq",)
+_REC_VECS = ("decay_up_t", "decay_bias", "gate_bias", "out_norm")
+_MOE_MATS = ("w_router", "w_gate_up", "w_down", "shared_gate_up", "shared_down")
+_MOE_VECS = ("correction",)
 
 
 def design_module(config):
@@ -37,39 +47,61 @@ def design_module(config):
     from . import kifusun
 
     return kifusun
+  if config.decoder_block == "gugidra":
+    from . import gugidra
+
+    return gugidra
   raise ValueError(f"decoder_block={config.decoder_block!r} is not a layered design")
 
 
 class LayeredParams:
-  """Device-resident weights of a layered model and the descriptor array handed to ``mtx_layered_create``."""
+  """Device-resident weights of a layered model: one entry per layer RUN of the plan (a layer that runs several times is listed
+  once per run; the runs share the device copy of every tensor that is the same host tensor)."""
 
   def __init__(self, plan: dict, config, device):
     fp32 = config.dtype == "float32"
     wt = torch.float32 if fp32 else torch.bfloat16
     self.float32 = fp32
     self.keep: List[torch.Tensor] = []
+    moved = {}  # id(host tensor) -> (host tensor, device tensor): shared weights are uploaded once
 
-    def mat(t):
-      t = t.to(device=device, dtype=wt).contiguous()
-      self.keep.append(t)
-      return t
-
-    def vec(t):
+    def put(t, dtype):
       if t is None:
         return None
-      t = t.to(device=device, dtype=torch.float32).contiguous()
-      self.keep.append(t)
-      return t
+      hit = moved.get((id(t), dtype))
+      if hit is not None:
+        return hit[1]
+      d = t.to(device=device, dtype=dtype).contiguous()
+      moved[(id(t), dtype)] = (t, d)
+      self.keep.append(d)
+      return d
+
+    mat = lambda t: put(t, wt)
+    vec = lambda t: put(t, torch.float32)
+
+    def pack(src, mats, vecs):
+      d = dict(src)
+      for k in mats:
+        if k in d:
+          d[k] = mat(d[k])
+      for k in vecs:
+        if k in d:
+          d[k] = vec(d[k])
+      return d
 
     self.embedding, self.head = mat(plan["embedding"]), mat(plan["head"])
     self.final_gain, self.embed_scale = float(plan["final_gain"]), float(plan["embed_scale"])
+    self.final_norm = vec(plan.get("final_norm"))
+    self.logit_softcap = float(plan.get("logit_softcap") or 0.0)
     self.layers = []
     for lp in plan["layers"]:
-      d = dict(lp)
-      for k in ("wqkv", "wo", "w_gate_up", "w_down"):
-        d[k] = mat(lp[k]) if lp[k] is not None else None
-      for k in ("bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk"):
-        d[k] = vec(lp.get(k))
+      d = pack(lp, _LAYER_MATS, _LAYER_VECS)
+      if d.get("attn"):
+        d["attn"] = pack(d["attn"], (), _ATTN_VECS)
+      if d.get("rec"):
+        d["rec"] = pack(d["rec"], (), _REC_VECS)
+      if d.get("moe"):
+        d["moe"] = pack(d["moe"], _MOE_MATS, _MOE_VECS)
       self.layers.append(d)
 
   def nbytes(self) -> int:
@@ -106,12 +138,17 @@ class LayeredEngine(MaxEngine):
     self._rng_state = torch.zeros(4, dtype=i32, device=dev)
     self._slot_ids = torch.arange(B, dtype=i32, device=dev)
     MP = self.page_manager.max_pages_per_group
-    self._page_map_dev = torch.zeros(B, MP, dtype=i32, device=dev)
+    # (row B of the map stays zero: rows of empty slots are parked in group B, whose keys land on the never-handed-out page 0
+    # and whose recurrent state nobody reads)
+    self._page_map_dev = torch.zeros(B + 1, MP, dtype=i32, device=dev)
     self._uploaded_map = None
-    # one pinned staging buffer per step: [token | group | pos | want | query tiles] rows
-    self._desc_host = torch.zeros(5 * self._max_rows + 8, dtype=i32).pin_memory()
-    self._desc_dev = torch.zeros(5 * self._max_rows + 8, dtype=i32, device=dev)
-    self._decode_tiles = torch.arange(B + 1, dtype=i32, device=dev)  # a decode step: every row is its own query tile
+    # one pinned staging buffer per step: [token | group | pos | want | query tiles | runs] rows
+    self._desc_host = torch.zeros(6 * self._max_rows + 16, dtype=i32).pin_memory()
+    self._desc_dev = torch.zeros(6 * self._max_rows + 16, dtype=i32, device=dev)
+    self._decode_tiles = torch.arange(B + 1, dtype=i32, device=dev)  # a decode step: every row is its own query tile and run
+    self._decode_groups = torch.arange(B, dtype=i32, device=dev)
+    self._states: List[tuple] = []
+    self._needs_runs = False
     self._sample_scratch = torch.zeros(5 * max(B, 1), dtype=torch.float32, device=dev)
     self._first_token = torch.zeros(1, dtype=i32, device=dev)
     self._first_log_prob = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -156,27 +193,77 @@ class LayeredEngine(MaxEngine):
     pm = self.page_manager
     ct = torch.float32 if lp.float32 else torch.bfloat16
     self._pools = []
+    self._states = []  # per layer run: the recurrent state tensors [state slots, ...] (fp32), or ()
     descs = (_lib.LayerDesc * len(lp.layers))()
     ptr = lambda t: t.data_ptr() if t is not None else None
-    for i, l in enumerate(lp.layers):
-      # (+1 page of slack behind the pool: the tensor-core attention reads whole 16-byte chunks of a row)
-      kp = torch.zeros(l["kv_heads"], pm.num_pages, pm.tokens_per_page, l["dim"], dtype=ct, device=dev)
-      vp = torch.zeros(l["kv_heads"], pm.num_pages, pm.tokens_per_page, l["vdim"], dtype=ct, device=dev)
+    slots = self.max_concurrent_decodes + 1  # (+ the parking slot of rows that belong to no live sequence)
+
+    def pools(G, d, dv):
+      kp = torch.zeros(G, pm.num_pages, pm.tokens_per_page, d, dtype=ct, device=dev)
+      vp = torch.zeros(G, pm.num_pages, pm.tokens_per_page, dv, dtype=ct, device=dev)
       self._pools.append((kp, vp))
+      return kp, vp
+
+    for i, l in enumerate(lp.layers):
       d = descs[i]
       d.mixer = _MIXERS[l["mixer"]]
-      for k in ("heads", "kv_heads", "dim", "vdim", "window", "value_mix", "ff"):
-        setattr(d, k, int(l[k]))
-      for k in ("scale", "softcap", "value_lambda", "gain1", "gain2"):
-        setattr(d, k, float(l[k]))
-      for k in ("wqkv", "bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk", "wo", "w_gate_up", "w_down"):
-        setattr(d, k, ptr(l[k]))
-      d.k_pages, d.v_pages = kp.data_ptr(), vp.data_ptr()
+      d.norm_style = _NORMS[l.get("norm_style", "out_gain")]
+      d.ff_kind = _FF_KINDS[l.get("ff_kind", "gelu")]
+      d.ff = int(l.get("ff", 0))
+      states = ()
+      if l["mixer"] == "window_sigmoid":
+        kp, vp = pools(l["kv_heads"], l["dim"], l["vdim"])
+        for k in ("heads", "kv_heads", "dim", "vdim", "window", "value_mix"):
+          setattr(d, k, int(l[k]))
+        for k in ("scale", "softcap", "value_lambda", "gain1", "gain2"):
+          setattr(d, k, float(l[k]))
+        for k in ("wqkv", "bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk"):
+          setattr(d, k, ptr(l[k]))
+        d.k_pages, d.v_pages = kp.data_ptr(), vp.data_ptr()
+      else:
+        d.n_in, d.add_embedding, d.ff_limit = int(l["n_in"]), int(l.get("add_embedding", 0)), float(l.get("ff_limit", 0.0))
+        for k in ("norm1", "norm1b", "norm2", "norm2b", "add_vector", "w_in", "b_in", "bo"):
+          setattr(d, k, ptr(l.get(k)))
+        a, r, m = l.get("attn"), l.get("rec"), l.get("moe")
+        if a:
+          kp, vp = pools(a["kv_heads"], a["dim"], a["vdim"])
+          for k in ("heads", "kv_heads", "dim", "vdim", "window", "rot_dims", "values_are_keys"):
+            setattr(d.attn, k, int(a[k]))
+          d.attn.scale, d.attn.out_scale = float(a["scale"]), float(a["out_scale"])
+          d.attn.rot_freq, d.attn.k_pages, d.attn.v_pages = ptr(a["rot_freq"]), kp.data_ptr(), vp.data_ptr()
+        else:
+          self._pools.append(())
+        if r:
+          d.rec.kind = _RECURRENCES[r["kind"]]
+          for k in ("heads", "dim", "vdim", "decay_rank", "gate_silu"):
+            setattr(d.rec, k, int(r[k]))
+          for k in ("q_scale", "tau", "gate_cap", "denom_eps", "out_scale"):
+            setattr(d.rec, k, float(r[k]))
+          for k in ("decay_up_t", "decay_bias", "gate_bias", "out_norm"):
+            setattr(d.rec, k, ptr(r.get(k)))
+          H, dk, dv = int(r["heads"]), int(r["dim"]), int(r["vdim"])
+          f32 = torch.float32
+          states = (torch.zeros(slots, H, dk, dv, dtype=f32, device=dev),)
+          d.rec.state_s = states[0].data_ptr()
+          if r["kind"] == "mlstm":
+            states += (torch.zeros(slots, H, dk, dtype=f32, device=dev), torch.zeros(slots, H, dtype=f32, device=dev))
+            d.rec.state_n, d.rec.state_m = states[1].data_ptr(), states[2].data_ptr()
+        if m:
+          for k in ("experts", "top", "groups", "keep_groups", "ff", "shared_ff"):
+            setattr(d.moe, k, int(m[k]))
+          d.moe.limit, d.moe.shared_limit = float(m["limit"]), float(m["shared_limit"])
+          for k in ("w_router", "correction", "w_gate_up", "w_down", "shared_gate_up", "shared_down"):
+            setattr(d.moe, k, ptr(m.get(k)))
+      for k in ("wo", "w_gate_up", "w_down"):
+        setattr(d, k, ptr(l.get(k)))
+      self._states.append(states)
+    self._needs_runs = any(l["mixer"] == "composite" for l in lp.layers)
     c = _lib.LayeredConfig(
         num_layers=len(lp.layers), width=int(cfg.emb_dim), vocab=int(cfg.vocab_size), float32=1 if lp.float32 else 0,
-        max_rows=self._max_rows, max_want=self._max_rows, num_groups=self.max_concurrent_decodes, num_pages=pm.num_pages,
+        max_rows=self._max_rows, max_want=self._max_rows, num_groups=slots, num_pages=pm.num_pages,
         tokens_per_page=pm.tokens_per_page, max_pages_per_group=pm.max_pages_per_group, eps=float(cfg.normalization_layer_epsilon),
-        embed_scale=lp.embed_scale, final_gain=lp.final_gain, embedding=lp.embedding.data_ptr(), head=lp.head.data_ptr())
+        embed_scale=lp.embed_scale, final_gain=lp.final_gain, embedding=lp.embedding.data_ptr(), head=lp.head.data_ptr(),
+        final_norm=ptr(lp.final_norm), logit_softcap=lp.logit_softcap)
     _lib.check(self.lib.mtx_layered_create(ctypes.byref(c), descs, ctypes.byref(self._handle)))
     ws = int(self.lib.mtx_layered_workspace_bytes(self._handle))
     self._ws = torch.empty(ws + 1024, dtype=torch.uint8, device=dev)
@@ -201,7 +288,8 @@ class LayeredEngine(MaxEngine):
     self._logits = torch.zeros(B, 1, V, dtype=torch.float32, device=self.device)
     self._state = {
         "logits": self._logits,
-        "cache": {"key_pages": [p[0] for p in self._pools], "value_pages": [p[1] for p in self._pools]},
+        "cache": {"key_pages": [p[0] for p in self._pools if p], "value_pages": [p[1] for p in self._pools if p],
+                  "recurrent_state": [t for st in self._states for t in st]},
         "next_pos": self._next_pos,
         "generated_tokens": self._generated,
         "tokens": self._tokens,
@@ -211,7 +299,7 @@ class LayeredEngine(MaxEngine):
   def _upload_page_map(self) -> None:
     ps = self.page_state
     if ps.page_map is not self._uploaded_map:
-      self._page_map_dev.copy_(torch.from_numpy(ps.page_map))
+      self._page_map_dev[: ps.page_map.shape[0]].copy_(torch.from_numpy(ps.page_map))
       self._uploaded_map = ps.page_map
 
   def _upload_page_state(self) -> None:  # (MaxEngine.release_pages calls it for device-resident page states; nothing to do here)
@@ -227,14 +315,17 @@ class LayeredEngine(MaxEngine):
     self.page_state = ps.replace(page_map=page_map)
     self._active[slot].zero_()
     self._next_pos[slot].zero_()
+    for st in self._states:  # (a sequence that starts at position 0 starts from zero anyway; this keeps a freed slot clean)
+      for t in st:
+        t[slot].zero_()
 
   # -- the ragged step ----------------------------------------------------------------------------
 
   def _run(self, rows: int, token_ptr: int, group_ptr: int, pos_ptr: int, n_want: int, want_ptr: int, logits: Optional[torch.Tensor],
-           n_tiles: int = 0, tiles_ptr: Optional[int] = None, graph: bool = False) -> None:
+           n_tiles: int = 0, tiles_ptr: Optional[int] = None, graph: bool = False, n_runs: int = 0, runs_ptr: Optional[int] = None) -> None:
     b = _lib.RaggedBatch(rows=rows, token=token_ptr, group=group_ptr, pos=pos_ptr, page_map=self._page_map_dev.data_ptr(), n_want=n_want,
                          want_rows=want_ptr if n_want else None, logits=logits.data_ptr() if n_want else None,
-                         n_tiles=n_tiles, tile_row0=tiles_ptr if n_tiles else None)
+                         n_tiles=n_tiles, tile_row0=tiles_ptr if n_tiles else None, n_runs=n_runs, run_row0=runs_ptr if n_runs else None)
     fn = self.lib.mtx_layered_step_graph if graph else self.lib.mtx_layered_step
     _lib.check(fn(self._handle, ctypes.byref(b), self._stream()))
 
@@ -288,18 +379,23 @@ class LayeredEngine(MaxEngine):
       if w:
         host[3 * R : 3 * R + len(w)] = torch.tensor(w, dtype=torch.int32)
       # query tiles: every run of consecutive positions (an entry, cut at the slice) in pieces of at most 16 rows
-      tiles = []
+      # and the runs themselves (recurrent mixers walk a run in order from its group's state)
+      tiles, cuts = [], []
       for a, b in runs:
         a, b = max(a, lo), min(b, hi)
+        if a < b:
+          cuts.append(a - lo)
         tiles.extend(range(a - lo, b - lo, QUERY_TILE_ROWS))
       tiles.append(n)
+      cuts.append(n)
       host[4 * R : 4 * R + len(tiles)] = torch.tensor(tiles, dtype=torch.int32)
+      host[5 * R + 8 : 5 * R + 8 + len(cuts)] = torch.tensor(cuts, dtype=torch.int32)
       if lo:
         torch.cuda.current_stream(self.device).synchronize()  # the previous slice has read the staging buffer
       self._desc_dev.copy_(host, non_blocking=True)
       p = self._desc_dev.data_ptr()
       dst = out[done_want : done_want + len(w)]
-      self._run(n, p, p + 4 * R, p + 8 * R, len(w), p + 12 * R, dst, len(tiles) - 1, p + 16 * R)
+      self._run(n, p, p + 4 * R, p + 8 * R, len(w), p + 12 * R, dst, len(tiles) - 1, p + 16 * R, n_runs=len(cuts) - 1, runs_ptr=p + 4 * (5 * R + 8))
       done_want += len(w)
     torch.cuda.current_stream(self.device).synchronize()  # the pinned staging buffer is free again when step returns
     return out
@@ -379,8 +475,10 @@ class LayeredEngine(MaxEngine):
       raise ValueError(f"the page pool is exhausted: slots {np.flatnonzero(grew).tolist()} cannot grow")
     self.page_state = ps
     self._upload_page_map()
-    self._run(B, self._tokens.data_ptr(), self._slot_ids.data_ptr(), self._next_pos.data_ptr(), B, self._slot_ids.data_ptr(), self._logits,
-              B, self._decode_tiles.data_ptr(), graph=self.use_cuda_graph)
+    # rows of empty slots are parked in group B: they must not touch the state of a slot that was prefilled but not yet inserted
+    torch.where(self._active.view(-1) != 0, self._slot_ids, torch.full_like(self._slot_ids, B), out=self._decode_groups)
+    self._run(B, self._tokens.data_ptr(), self._decode_groups.data_ptr(), self._next_pos.data_ptr(), B, self._slot_ids.data_ptr(), self._logits,
+              B, self._decode_tiles.data_ptr(), graph=self.use_cuda_graph, n_runs=B, runs_ptr=self._decode_tiles.data_ptr())
     self._sample(self._logits.view(B, -1), B, self._tokens, self._log_prob, 0)
     # bookkeeping of maxengine.py:913-928 for the occupied slots (empty ones stay at position 0 on page 0)
     self._next_pos.add_(self._active)

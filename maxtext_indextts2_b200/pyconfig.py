@@ -36,8 +36,8 @@ _VALID_SAMPLING = ("greedy", "weighted", "nucleus", "topk")
 _VALID_AXIS_ORDER = ("0,1,2,3", "0,2,1,3")
 # Designs whose layers are listed one by one (`layer_specs`) and run on the layered engine (layered_engine.py), keyed by
 # decoder_block; ARCHITECTURES maps the "architecture" of a model folder's config.json to the block.
-LAYERED_BLOCKS = ("kifusun",)
-ARCHITECTURES = {"Kifusun": "kifusun"}
+LAYERED_BLOCKS = ("kifusun", "gugidra")
+ARCHITECTURES = {"Kifusun": "kifusun", "Gugidra": "gugidra"}
 
 
 def _string_to_bool(s: str) -> bool:
@@ -122,6 +122,12 @@ def _validate_layered(keys: dict) -> None:
     from . import kifusun
 
     kifusun.validate_layer_specs(keys["layer_specs"])
+  if keys["decoder_block"] == "gugidra":
+    from . import gugidra
+
+    gugidra.validate_layer_specs(keys["layer_specs"], keys["layer_loop"])
+  elif keys["layer_loop"]:
+    raise ValueError("layer_loop belongs to designs that repeat a span of layers")
 
 
 def _validate(keys: dict) -> None:
@@ -176,8 +182,8 @@ def _validate(keys: dict) -> None:
       raise ValueError("only mlp_activations=[silu, linear] is on this path")
     if keys["use_post_attn_norm"] or keys["use_post_ffw_norm"] or keys["sliding_window_size"]:
       raise ValueError("use_post_attn_norm / use_post_ffw_norm / sliding_window_size belong to the gemma3 block")
-  if keys["layer_specs"] or keys["model_dir"]:
-    raise ValueError("layer_specs / model_dir belong to the layered designs")
+  if keys["layer_specs"] or keys["model_dir"] or keys["layer_loop"]:
+    raise ValueError("layer_specs / layer_loop / model_dir belong to the layered designs")
   if keys["max_target_length"] <= keys["max_prefill_predict_length"]:
     # inference/kvcache.py:408-412
     raise ValueError(
@@ -282,6 +288,10 @@ def from_model_dict(model: dict, **overrides) -> HyperParameters:
     from . import kifusun
 
     keys = kifusun.config_keys(model)
+  elif block == "gugidra":
+    from . import gugidra
+
+    keys = gugidra.config_keys(model)
   keys.update(decoder_block=block, attention="paged", scan_layers=False, weight_dtype="bfloat16")
   keys.update(overrides)
   if "max_prefill_predict_length" not in overrides:  # any prompt that fits the sequence
