@@ -50,6 +50,7 @@ def layer_runs(n_layers: int, loop: Optional[dict]) -> List[Tuple[int, int, bool
 def config_keys(model: dict) -> dict:
   """config.json of a Gugidra model -> keys of configs/base.yml."""
   layers = model["layers"]
+  validate_layer_specs(layers, model.get("loop"))
   ffs = []
   for l in layers:
     f = l.get("mlp")

@@ -240,3 +240,68 @@ class GugidraRef:
     cap = float(self.c["logit_softcap"])
     z = wnorm(x, t["final.norm"], eps) @ t["head"].T
     return cap * np.tanh(z / cap) if cap else z
+
+
+def logits_of(config: dict, tensors: dict, tokens) -> np.ndarray:
+  """The logits [T, vocab] of one sequence fed at once."""
+  ref = GugidraRef(config, tensors)
+  return ref.forward(list(tokens), ref.new_state())
+
+
+def on_bf16_grid(a) -> np.ndarray:
+  """`a` rounded (to nearest, ties to even) to numbers that bfloat16 represents exactly, as float64."""
+  u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+  u = (u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+  return u.view(np.float32).astype(F)
+
+
+def random_model(config: dict, seed: int = 0, rank: int = 5) -> dict:
+  """Random weights with the design's tensor names as float64 arrays that are exactly representable in bfloat16, so that an
+  engine loading them as bfloat16 computes with the same numbers."""
+  rng = np.random.Generator(np.random.PCG64(seed))
+  E, V = int(config["width"]), int(config["vocab"])
+  rn = lambda *shape, std=1.0, mean=0.0: rng.standard_normal(shape) * std + mean
+  lin = lambda n, k: rn(n, k, std=k**-0.5)
+  t = {"embed": rn(V, E), "final.norm": rn(E, std=0.2), "head": lin(V, E)}
+  if config.get("loop"):
+    t["loop.step"] = rn(int(config["loop"]["times"]), E, std=0.5)
+  for i, l in enumerate(config["layers"]):
+    p, m = f"l{i}.", l["mixer"]
+    for n in ("norm1", "norm1b", "norm2", "norm2b"):
+      t[p + n] = rn(E, std=0.2)
+    if l["type"] == "gla":
+      H, d, dv = m["heads"], m["dim"], m["vdim"]
+      q = p + "mix."
+      t[q + "q"], t[q + "k"], t[q + "v"], t[q + "g"] = lin(H * d, E), lin(H * d, E), lin(H * dv, E), lin(H * dv, E)
+      t[q + "o"], t[q + "norm"] = lin(E, H * dv), rn(dv, std=0.2, mean=1.0)
+      t[q + "a1"], t[q + "a2"], t[q + "a2.b"] = lin(rank, E), rn(H * d, rank, std=1.0), rn(H * d, std=1.5, mean=1.0)
+    else:
+      a, r = m["left"], m["right"]
+      H, G, d = a["heads"], a["kv_heads"], a["dim"]
+      q = p + "mix.left."
+      t[q + "q"], t[q + "k"], t[q + "o"] = lin(H * d, E), lin(G * d, E), lin(E, H * d)
+      t[q + "q.b"], t[q + "k.b"], t[q + "o.b"] = rn(H * d, std=0.3), rn(G * d, std=0.3), rn(E, std=0.3)
+      Hr, dr, dvr = r["heads"], r["dim"], r["vdim"]
+      q = p + "mix.right."
+      t[q + "q"], t[q + "k"], t[q + "v"], t[q + "g"] = lin(Hr * dr, E), lin(Hr * dr, E), lin(Hr * dvr, E), lin(Hr * dvr, E)
+      t[q + "o"], t[q + "norm"] = lin(E, Hr * dvr), rn(Hr * dvr, std=0.2, mean=1.0)
+      t[q + "i"], t[q + "f"] = lin(Hr, E) * 2.0, lin(Hr, E) * 2.0
+      t[q + "i.b"], t[q + "f.b"] = rn(Hr, std=1.0), rn(Hr, std=1.0, mean=2.0)
+    f = l.get("mlp")
+    if not f:
+      continue
+    q = p + "mlp."
+
+    def gated(prefix, n):
+      t[prefix + "gate"], t[prefix + "up"], t[prefix + "down"] = lin(n, E) * 2.0, lin(n, E) * 2.0, lin(E, n)
+
+    if f["kind"] == "dense":
+      gated(q, f["ff"])
+    else:
+      n_exp = f["router"]["experts"]
+      for e in range(n_exp):
+        gated(f"{q}e{e}.", f["expert"]["ff"])
+      t[q + "router"], t[q + "correction"] = lin(n_exp, E) * 3.0, rn(n_exp, std=0.3)
+      if f.get("shared"):
+        gated(q + "shared.", f["shared"]["ff"])
+  return {k: on_bf16_grid(v) for k, v in t.items()}
