@@ -66,6 +66,7 @@ def parse_args():
   ap.add_argument("--no-verify", action="store_true", help="skip the oracle check of one step of the timed state")
   ap.add_argument("--prompt-len", type=int, default=4000, help="--mode prefill: prompt tokens (BASELINE configs[3]: 4000 of P = 4096)")
   ap.add_argument("--size", default="all", help="--mode layered: one of the sizes of LAYERED_SIZES, or all")
+  ap.add_argument("--design", default="kifusun", choices=["kifusun", "gugidra"], help="--mode layered: the layered design that is measured beside gemma3")
   ap.add_argument("--mode", default="batch", choices=["batch", "vocab-parallel", "prefill", "layered"],
                   help="batch: request-batch partitioned, no collective (default); vocab-parallel: every GPU decodes the same --batch slots, "
                        "the logits projection is sharded over the GPUs and one NCCL all-gather carries the per-shard candidates")
@@ -610,11 +611,12 @@ def _time_ms(fn, steps, warmup):
 
 
 def run_layered(args):
-  """--mode layered: prefill and decode throughput of the Kifusun design on the layered engine beside the gemma3 block (the
-  closest existing model: sliding window, q/k norm, soft cap, gelu-gated feed-forward, norms on the sublayer outputs) at equal
-  layer sizes, both through MaxEngine.  One JSON line per size."""
-  from maxtext_indextts2_b200 import kifusun, maxengine, pyconfig
+  """--mode layered: prefill and decode throughput of a layered design (--design) on the layered engine beside the gemma3 block
+  (the closest existing model: softmax attention with rotary positions and grouped key heads, norms before and after every
+  sublayer, gated feed-forward) at equal layer sizes, both through MaxEngine.  One JSON line per size."""
+  from maxtext_indextts2_b200 import gugidra, kifusun, maxengine, pyconfig
 
+  D = args.design  # (the keys of the output line carry the design's name)
   names = list(LAYERED_SIZES) if args.size == "all" else [args.size]
   steps, warmup = max(1, min(args.steps, 10)), max(3, min(args.warmup, 5))
   for name in names:
@@ -624,9 +626,19 @@ def run_layered(args):
     tpp = 64
     out = {"metric": "layered model: prefill tokens/s and decode tokens/s beside gemma3 at equal size", "mode": "layered", "size": name, "geometry": z,
            "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic, random weights", "l2": "flushed between timed iterations"}
-    # ---- Kifusun ----
-    layers = [kifusun.attention_layer(z["heads"], z["kv_heads"], z["dim"], z["dim"], z["window"], ff=z["ff"], bias_max=float(z["window"])) for _ in range(L)]
-    model = kifusun.model_dict(z["width"], z["vocab"], layers, embed_scale=1.0)
+    # ---- the layered design ----
+    if D == "kifusun":
+      layers = [kifusun.attention_layer(z["heads"], z["kv_heads"], z["dim"], z["dim"], z["window"], ff=z["ff"], bias_max=float(z["window"])) for _ in range(L)]
+      model = kifusun.model_dict(z["width"], z["vocab"], layers, embed_scale=1.0)
+    else:
+      # Gugidra at the same sizes: attention + mLSTM layers and GLA layers in turn; the attention has gemma3's heads (no window: the
+      # design has none), the recurrences half as many key channels per head; dense feed-forwards of gemma3's size in turn with
+      # routed ones of the same active size (16 experts of ff / 8, four per token, a shared expert of ff / 2)
+      H, G, d, F = z["heads"], z["kv_heads"], z["dim"], z["ff"]
+      ffs = [gugidra.dense_ff(F), gugidra.moe_ff(16, 4, F // 8, groups=4, keep=2, shared_ff=F // 2)]
+      layers = [gugidra.parallel_layer(H, G, d, H // 2, d // 2, d, mlp=ffs[(i // 2) % 2]) if i % 2 == 0 else gugidra.gla_layer(H, d // 2, d, mlp=ffs[((i + 1) // 2) % 2])
+                for i in range(L)]
+      model = gugidra.model_dict(z["width"], z["vocab"], layers)
     pages = B * ((C + 8 + tpp - 1) // tpp) + (P + tpp - 1) // tpp + 2
     cfg = pyconfig.from_model_dict(model, dtype="bfloat16", per_device_batch_size=B, max_target_length=T, pagedattn_tokens_per_page=tpp,
                                    pagedattn_num_pages=pages, max_step_rows=max(P, B))
@@ -641,8 +653,8 @@ def run_layered(args):
 
     n0 = engine.lib.mtx_launch_count()
     ms = _time_ms(k_prefill, steps, warmup)
-    out["kifusun_prefill_ms"], out["kifusun_prefill_tokens_per_s"] = ms, P / ms * 1e3
-    out["kifusun_prefill_launches"] = int(engine.lib.mtx_launch_count() - n0) // (steps + warmup)
+    out[D + "_prefill_ms"], out[D + "_prefill_tokens_per_s"] = ms, P / ms * 1e3
+    out[D + "_prefill_launches"] = int(engine.lib.mtx_launch_count() - n0) // (steps + warmup)
     engine.release_pages(0)
     ctx = torch.randint(0, z["vocab"], (C,), generator=torch.Generator().manual_seed(2)).tolist()
     for slot in range(B):  # every slot holds a C-token context (the same tokens: only the cache traffic matters)
@@ -653,7 +665,7 @@ def run_layered(args):
       engine.generate(params, state)
 
     ms = _time_ms(k_decode, min(steps, 6), 3)
-    out["kifusun_decode_ms"], out["kifusun_decode_tokens_per_s"] = ms, B / ms * 1e3
+    out[D + "_decode_ms"], out[D + "_decode_tokens_per_s"] = ms, B / ms * 1e3
     del engine, params, state
     torch.cuda.empty_cache()
     # ---- gemma3 block at the same sizes (every layer but each sixth is a sliding-window layer) ----

@@ -494,6 +494,34 @@ int sandwich_step(mtx_layered* e, const float* y, const float* bias, const float
   return launch(sandwich_step_kernel<T>, dim3(rows), dim3(256), 0, st, sa, static_cast<T*>(e->xa));
 }
 
+bool use_softmax_mma() {
+  static int on = env_int("MTX_SOFTMAX_MMA", 1);
+  return on != 0;
+}
+
+template <int D16, int PARTS, int KT>
+int launch_softmax_mma_t(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan& plan, int n_tiles, cudaStream_t st) {
+  static size_t have = 0;  // per instantiation
+  if (plan.smem > 48 * 1024 && plan.smem > have) {
+    MTX_CUDA(cudaFuncSetAttribute(softmax_attention_mma_kernel<D16, PARTS, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(plan.smem)));
+    have = plan.smem;
+  }
+  return launch(softmax_attention_mma_kernel<D16, PARTS, KT>, dim3(n_tiles, sa.kv_heads * plan.chunks), dim3(plan.warps * 32), plan.smem, st, sa, plan.chunks);
+}
+
+int launch_softmax_mma(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan& plan, int n_tiles, cudaStream_t st) {
+  switch (plan.d16) {
+    case 1: return launch_softmax_mma_t<1, 1, 64>(sa, plan, n_tiles, st);
+    case 2: return launch_softmax_mma_t<2, 1, 64>(sa, plan, n_tiles, st);
+    case 3: return launch_softmax_mma_t<3, 1, 64>(sa, plan, n_tiles, st);
+    case 4: return launch_softmax_mma_t<4, 1, 64>(sa, plan, n_tiles, st);
+    case 6: return launch_softmax_mma_t<6, 1, 64>(sa, plan, n_tiles, st);
+    case 8: return launch_softmax_mma_t<8, 1, 64>(sa, plan, n_tiles, st);
+    case 16: return launch_softmax_mma_t<16, 2, 32>(sa, plan, n_tiles, st);
+  }
+  return fail(MTX_ERR_UNSUPPORTED, "no tensor-core attention for dim %d", sa.dim);
+}
+
 // a MTX_MIXER_COMPOSITE layer with MTX_NORM_SANDWICH norms; xa holds wnorm(x, norm1) on entry
 template <typename T>
 int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_t st) {
@@ -552,6 +580,14 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
     sa.max_pages = c.max_pages_per_group;
     sa.scale = a.scale;
     sa.out_scale = a.out_scale;
+    bool done = false;
+    if constexpr (sizeof(T) == 2) {
+      const SoftmaxMmaPlan plan = softmax_mma_plan(a.heads, a.kv_heads, a.dim, a.vdim);
+      if (plan.ok && use_softmax_mma() && cc.k_out % 2 == 0) {
+        MTX_TRY(launch_softmax_mma(sa, plan, b.n_tiles, st));
+        done = true;
+      }
+    }
     const size_t smem = softmax_attn_smem_bytes(a.dim, a.vdim);
     static size_t attr_bytes[2] = {0, 0};  // per instantiation (bf16, float)
     size_t& have = attr_bytes[sizeof(T) == 4 ? 1 : 0];
@@ -559,7 +595,7 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
       MTX_CUDA(cudaFuncSetAttribute(softmax_attention_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
       have = smem;
     }
-    MTX_TRY(launch(softmax_attention_rows_kernel<T>, dim3(b.n_tiles, a.heads), dim3(kSmaxThreads), smem, st, sa));
+    if (!done) MTX_TRY(launch(softmax_attention_rows_kernel<T>, dim3(b.n_tiles, a.heads), dim3(kSmaxThreads), smem, st, sa));
   }
   if (l.rec.kind != 0) {
     const mtx_recurrent_desc& r = l.rec;

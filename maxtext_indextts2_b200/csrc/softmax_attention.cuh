@@ -14,13 +14,17 @@
 //   softmax_attention_rows_kernel<T>   one CTA per (query tile of <= 16 rows of one sequence, query head); keys walked in tiles
 //                              staged as fp32 in shared memory; running maximum and sum per row; everything fp32 (T is only the
 //                              dtype of q, the pools and the output).  Serves float32 engines, every geometry, and decode rows.
-//   softmax_attention_mma_kernel       bf16: the same work item on mma.sync m16n8k16 (S = Q K^T and O += P V), for dim and vdim
-//                              that are multiples of 16.
+//   softmax_attention_mma_kernel       bf16: one CTA per (query tile, key head); a warp per (query head of the group, slice of the
+//                              value columns); S = Q K^T and O += P V on mma.sync m16n8k16 with fp32 accumulators, scores, running
+//                              maximum and sum in fp32 registers, K / V tiles double-buffered in shared memory by cp.async through the
+//                              page map.  For vdim == dim in {16, 32, 48, 64, 96, 128, 256}.
 #pragma once
 
 #include "common.cuh"
 #include "layer_ops.cuh"
 #include "linear_any.cuh"
+#include "window_attention_mma.cuh"     // mma_bf16_16816, cp_async_16
+#include "window_attention_decode.cuh"  // cp_async_commit, cp_async_wait_pending
 
 namespace mtx {
 
@@ -199,6 +203,193 @@ __global__ void __launch_bounds__(kSmaxThreads) softmax_attention_rows_kernel(co
       const int i = o / dv, c = o % dv;
       a.out[size_t(r0 + i) * a.ld_out + h * dv + c] = to_act<T>(acc[u] * a.out_scale / s_sum[i]);
     }
+  }
+}
+
+// ---- bf16 tensor-core arm ------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smax_pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+struct SoftmaxMmaPlan {
+  bool ok;
+  int d16, parts, key_tile, warps, chunks;  // chunks: CTAs per (tile, key head), each with `warps` warps
+  size_t smem;
+};
+
+// D16 = dim / 16 (vdim == dim); PARTS = slices of the value columns, a warp each (keeps the output accumulators in registers)
+inline SoftmaxMmaPlan softmax_mma_plan(int heads, int kv_heads, int dim, int vdim) {
+  SoftmaxMmaPlan p = {false, 0, 1, 64, 1, 1, 0};
+  if (dim != vdim || dim % 16 != 0) return p;
+  const int d16 = dim / 16;
+  if (!(d16 == 1 || d16 == 2 || d16 == 3 || d16 == 4 || d16 == 6 || d16 == 8 || d16 == 16)) return p;
+  p.ok = true;
+  p.d16 = d16;
+  p.parts = d16 == 16 ? 2 : 1;
+  p.key_tile = d16 == 16 ? 32 : 64;
+  const int units = (heads / kv_heads) * p.parts;  // warps' worth of work per (tile, key head)
+  p.warps = units < 4 ? units : 4;
+  p.chunks = (units + p.warps - 1) / p.warps;
+  p.smem = size_t(2) * p.key_tile * 2 * (dim + 8) * sizeof(bf16);
+  return p;
+}
+
+template <int D16, int PARTS, int KT>
+__global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const SoftmaxAttnArgs<bf16> a, int chunks) {
+  extern __shared__ __align__(16) unsigned char smax_raw[];
+  constexpr int D = 16 * D16, PITCH = D + 8, DVW = D / PARTS, NB = DVW / 8;  // NB: 8-column blocks of a warp's output
+  bf16* const stage0 = reinterpret_cast<bf16*>(smax_raw);                     // stage s: K [KT][PITCH], then V [KT][PITCH]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3, nthreads = blockDim.x, nwarps = nthreads >> 5;
+  griddep_wait();
+  const int rep = a.heads / a.kv_heads;
+  const int kvh = blockIdx.y / chunks, unit = (blockIdx.y % chunks) * nwarps + warp;  // unit = (head of the group, part)
+  const bool active = unit < rep * PARTS;
+  const int h = kvh * rep + (active ? unit / PARTS : 0), part = active ? unit % PARTS : 0;
+  const int r0 = a.tile_row0[blockIdx.x], nr = a.tile_row0[blockIdx.x + 1] - r0;
+  const int p0 = a.pos[r0], grp = a.group[r0], p_last = p0 + nr - 1;
+  int lo = 0;
+  if (a.window > 0 && p0 - a.window + 1 > 0) lo = p0 - a.window + 1;
+  const int* pages = a.page_map + size_t(grp) * a.max_pages;
+  const size_t head_rows = size_t(kvh) * a.num_pages * a.tokens_per_page;
+  const int n_key_tiles = (p_last - lo) / KT + 1;
+
+  auto load_tile = [&](int it, int stage) {
+    bf16* sk = stage0 + size_t(stage) * 2 * KT * PITCH;
+    bf16* sv = sk + KT * PITCH;
+    const int j0 = lo + it * KT;
+    constexpr int CH = D / 8;  // 16-byte chunks per row
+    for (int e = tid; e < KT * CH; e += nthreads) {
+      const int jj = e / CH, c = e % CH, j = j0 + jj;
+      const bool ok = j <= p_last;
+      const size_t row = ok ? head_rows + size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page : 0;
+      cp_async_16(sk + jj * PITCH + c * 8, a.k_pages + row * D + c * 8, ok);
+      cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + row * D + c * 8, ok);
+    }
+    cp_async_commit();
+  };
+
+  // Q fragments of rows g and g + 8 (rows beyond the tile: zero)
+  uint32_t qf[D16][4];
+  {
+    const bf16* q0 = a.q + size_t(r0 + g) * a.heads * D + h * D;
+    const bf16* q1 = q0 + size_t(8) * a.heads * D;
+    const bool ok0 = active && g < nr, ok1 = active && g + 8 < nr;
+#pragma unroll
+    for (int kk = 0; kk < D16; ++kk) {
+      qf[kk][0] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
+      qf[kk][1] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 2 * t) : 0u;
+      qf[kk][2] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
+      qf[kk][3] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + 2 * t) : 0u;
+    }
+  }
+  float o[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nb][e] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  const int pi0 = p0 + g, pi1 = p0 + g + 8;
+
+  load_tile(0, 0);
+  for (int it = 0; it < n_key_tiles; ++it) {
+    if (it + 1 < n_key_tiles) {
+      load_tile(it + 1, (it + 1) & 1);
+      cp_async_wait_pending(1);
+    } else {
+      cp_async_wait_pending(0);
+    }
+    __syncthreads();
+    if (active) {
+      const bf16* sk = stage0 + size_t(it & 1) * 2 * KT * PITCH;
+      const bf16* sv = sk + KT * PITCH;
+      const int j0 = lo + it * KT;
+      float s[KT / 8][4];
+#pragma unroll
+      for (int nb = 0; nb < KT / 8; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nb][e] = 0.0f;
+        const bf16* kr = sk + (nb * 8 + g) * PITCH + 2 * t;
+#pragma unroll
+        for (int kk = 0; kk < D16; ++kk)
+          mma_bf16_16816(s[nb], qf[kk], *reinterpret_cast<const uint32_t*>(kr + kk * 16), *reinterpret_cast<const uint32_t*>(kr + kk * 16 + 8));
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int nb = 0; nb < KT / 8; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + nb * 8 + 2 * t + (e & 1), pi = (e & 2) ? pi1 : pi0;
+          const bool seen = j <= pi && (a.window <= 0 || pi - j < a.window);
+          s[nb][e] = seen ? s[nb][e] * a.scale : -INFINITY;
+        }
+        mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+      const float base0 = mn0 == -INFINITY ? 0.0f : mn0, base1 = mn1 == -INFINITY ? 0.0f : mn1;
+      const float fix0 = __expf(m_run[0] - base0), fix1 = __expf(m_run[1] - base1);  // (exp(-inf) = 0 while a row has seen no key)
+      m_run[0] = mn0;
+      m_run[1] = mn1;
+      float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+      for (int nb = 0; nb < KT / 8; ++nb) {
+        s[nb][0] = __expf(s[nb][0] - base0);
+        s[nb][1] = __expf(s[nb][1] - base0);
+        s[nb][2] = __expf(s[nb][2] - base1);
+        s[nb][3] = __expf(s[nb][3] - base1);
+        sum0 += s[nb][0] + s[nb][1];
+        sum1 += s[nb][2] + s[nb][3];
+      }
+      l_run[0] = l_run[0] * fix0 + sum0;  // (per-thread partial sums; the four lanes of a row are added at the end)
+      l_run[1] = l_run[1] * fix1 + sum1;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        o[nb][0] *= fix0;
+        o[nb][1] *= fix0;
+        o[nb][2] *= fix1;
+        o[nb][3] *= fix1;
+      }
+#pragma unroll
+      for (int kk = 0; kk < KT / 16; ++kk) {
+        uint32_t pf[4];
+        pf[0] = smax_pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pf[1] = smax_pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pf[2] = smax_pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pf[3] = smax_pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        // V [key][column] -> the B fragments of two 8-column blocks at once: lanes 0-15 name the 16 key rows of the first block,
+        // lanes 16-31 those of the second
+        const bf16* vrow = sv + (kk * 16 + (lane & 15)) * PITCH + part * DVW + (lane >> 4) * 8;
+#pragma unroll
+        for (int nb = 0; nb < NB; nb += 2) {
+          uint32_t b0, b1, b2, b3;
+          const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(vrow + nb * 8));
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+          mma_bf16_16816(o[nb], pf, b0, b1);
+          mma_bf16_16816(o[nb + 1], pf, b2, b3);
+        }
+      }
+    }
+    __syncthreads();  // the stage is free for the load after next
+  }
+  if (!active) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  const float f0 = a.out_scale / l_run[0], f1 = a.out_scale / l_run[1];
+  bf16* out0 = a.out + size_t(r0 + g) * a.ld_out + h * D + part * DVW + 2 * t;
+  bf16* out1 = out0 + size_t(8) * a.ld_out;
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    if (g < nr) *reinterpret_cast<uint32_t*>(out0 + nb * 8) = smax_pack_bf16(o[nb][0] * f0, o[nb][1] * f0);
+    if (g + 8 < nr) *reinterpret_cast<uint32_t*>(out1 + nb * 8) = smax_pack_bf16(o[nb][2] * f1, o[nb][3] * f1);
   }
 }
 

@@ -146,6 +146,7 @@ def layer_plan(config, tensors: Dict[str, torch.Tensor], i: int) -> Dict[str, An
   spec = config.layer_specs[i]
   E = int(config.emb_dim)
   t, p = tensors, f"l{i}.mix."
+  dev = tensors["embed"].device
   f32 = lambda name: t[name].to(torch.float32)
   rows: List[torch.Tensor] = []
   bias: List[torch.Tensor] = []
@@ -158,7 +159,7 @@ def layer_plan(config, tensors: Dict[str, torch.Tensor], i: int) -> Dict[str, An
       bias.append(_shape(f32(name + ".b"), (n,), name + ".b"))
       has_bias = True
     else:
-      bias.append(torch.zeros(n, dtype=torch.float32))
+      bias.append(torch.zeros(n, dtype=torch.float32, device=dev))
 
   plan: Dict[str, Any] = dict(mixer="composite", norm_style="sandwich", attn=None, rec=None, ff_kind="none", ff=0, moe=None, bo=None)
   wo: List[torch.Tensor] = []
@@ -178,7 +179,7 @@ def layer_plan(config, tensors: Dict[str, torch.Tensor], i: int) -> Dict[str, An
     for name, n in (("q", Hr * dr), ("k", Hr * dr), ("v", Hr * dvr), ("g", Hr * dvr)):
       add(q + name, n)
     rows.append(torch.cat([_shape(t[q + "i"], (Hr, E), q + "i"), _shape(t[q + "f"], (Hr, E), q + "f")], dim=0))
-    bias.append(torch.zeros(2 * Hr, dtype=torch.float32))  # (the gates' biases are added in fp32 by the recurrence)
+    bias.append(torch.zeros(2 * Hr, dtype=torch.float32, device=dev))  # (the gates' biases are added in fp32 by the recurrence)
     plan["rec"] = dict(kind="mlstm", heads=Hr, dim=dr, vdim=dvr, decay_rank=0, gate_silu=0, q_scale=dr**-0.5, tau=1.0,
                        gate_cap=float(r["gate_cap"]), denom_eps=MLSTM_DENOM_EPS, out_scale=rs,
                        gate_bias=torch.cat([_shape(f32(q + "i.b"), (Hr,), q + "i.b"), _shape(f32(q + "f.b"), (Hr,), q + "f.b")]),
@@ -199,8 +200,8 @@ def layer_plan(config, tensors: Dict[str, torch.Tensor], i: int) -> Dict[str, An
   w_in, b_in = torch.cat(rows, dim=0), torch.cat(bias)
   pad = (-w_in.shape[0]) % TILE_ROWS
   if pad and E % 64 == 0:
-    w_in = torch.cat([w_in, torch.zeros(pad, E, dtype=w_in.dtype)], dim=0)
-    b_in = torch.cat([b_in, torch.zeros(pad)])
+    w_in = torch.cat([w_in, torch.zeros(pad, E, dtype=w_in.dtype, device=dev)], dim=0)
+    b_in = torch.cat([b_in, torch.zeros(pad, device=dev)])
   plan.update(w_in=w_in, b_in=b_in if has_bias else None, n_in=int(w_in.shape[0]), wo=torch.cat(wo, dim=1))
   for n in ("norm1", "norm1b"):
     plan[n] = _shape(f32(f"l{i}.{n}"), (E,), f"l{i}.{n}")

@@ -363,6 +363,35 @@ def test_bfloat16_engine_is_within_rounding_of_the_exact_model(case):
   assert rms_err(np.concatenate(got), want) < 3e-2
 
 
+# ---- the tensor-core attention (bf16, head sizes in multiples of 16) ------------------------------------------------------------------
+
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(4, 2, 64, 16), (2, 2, 16, 8), (8, 1, 32, 64), (6, 2, 48, 4), (5, 1, 96, 16), (4, 4, 128, 32), (2, 1, 256, 16)])
+def test_tensor_core_attention_shapes_and_schedules(heads, kv_heads, dim, page):
+  """Every head size of the tensor-core arm, one to eight query heads per key head (several CTAs per key head beyond four
+  warps), prompts in portions that end inside, at and after the 64-key (32-key) tiles, 16-row query tiles that start anywhere,
+  then single tokens; peaky scores so that single far keys matter."""
+  cfg = model([par(heads=heads, kv_heads=kv_heads, dim=dim, rot_dims=dim // 2, r_heads=1, r_dim=16, r_vdim=16, right_scale=0.1),
+               par(g.dense_ff(32, 2.0), heads=heads, kv_heads=kv_heads, dim=dim, rot_dims=dim, r_heads=1, r_dim=16, r_vdim=16)], width=64, vocab=90, softcap=0.0)
+  t = _peaky(cfg, seed=dim + heads)
+  n = 150
+  toks = tokens_for(cfg, n, seed=dim)
+  want = ref.logits_of(cfg, t, toks)
+  engine = make_engine(cfg, t, dtype="bfloat16", tokens_per_page=page, num_pages=2 * (n // page + 2) + 2, max_len=n + 8)
+  assert rms_err(whole(engine, toks), want) < 3e-2
+  for cuts in ([63, 1, 1, 30, 33], [64, 64], [65, 5, 58, 9], [31, 2, 31, 33, 7, 25]):
+    got, at = [], 0
+    for c in cuts:
+      got.append(engine.step([(1, toks[at : at + c], list(range(c)))]).cpu().numpy())
+      at += c
+    got += [engine.step([(1, [tok], [0])]).cpu().numpy() for tok in toks[at : at + 6]]
+    engine.release_pages(1)
+    assert rms_err(np.concatenate(got), want[: at + 6]) < 3e-2, cuts
+  # two sequences side by side, one in the middle of its prompt, one decoding
+  engine.step([(0, toks[:70], []), (2, toks[:101], [])])
+  out = engine.step([(0, toks[70:90], list(range(20))), (2, [toks[101]], [0])]).cpu().numpy()
+  assert rms_err(out, np.concatenate([want[70:90], want[101:102]])) < 3e-2
+
+
 # ---- the framework's entry point: scheduler, sampler -------------------------------------------------------------------------------
 
 def test_greedy_generation_through_the_offline_engine():
