@@ -656,10 +656,7 @@ def run_layered(args):
     out[D + "_prefill_ms"], out[D + "_prefill_tokens_per_s"] = ms, P / ms * 1e3
     out[D + "_prefill_launches"] = int(engine.lib.mtx_launch_count() - n0) // (steps + warmup)
     engine.release_pages(0)
-    ctx = torch.randint(0, z["vocab"], (C,), generator=torch.Generator().manual_seed(2)).tolist()
-    for slot in range(B):  # every slot holds a C-token context (the same tokens: only the cache traffic matters)
-      prefix, _ = engine.prefill(params=params, padded_tokens=torch.tensor(ctx), true_length=C, slot=slot)
-      state = engine.insert(prefix, state, slot)
+    state = engine.fill_synthetic_context([C] * B)  # every slot holds a C-token context (only the cache and state traffic matters)
 
     def k_decode():
       engine.generate(params, state)
@@ -694,6 +691,10 @@ def main():
     run_reference_arm(args)
     return
   if args.mode == "layered":
+    from maxtext_indextts2_b200 import _lib as lib_build
+
+    if lib_build.needs_build():
+      lib_build.build()
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     run_layered(args)
     return

@@ -409,7 +409,7 @@ typedef struct {
   const float* decay_bias; /* GLA: [heads*dim] */
   const float* gate_bias;  /* mLSTM: [2*heads] input gates, then forget gates */
   const float* out_norm;   /* [heads*vdim]: o is divided by its per-head root mean square, then multiplied by this */
-  float* state_s;          /* [state slots, heads, dim, vdim] */
+  float* state_s;          /* [state slots, heads, vdim, dim] (a value column's key channels are contiguous) */
   float* state_n;          /* mLSTM: [state slots, heads, dim] */
   float* state_m;          /* mLSTM: [state slots, heads] */
 } mtx_recurrent_desc;

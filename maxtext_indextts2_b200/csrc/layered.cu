@@ -40,6 +40,8 @@ struct mtx_layered {
   cudaStream_t cap_stream = nullptr;
   float* attn_part = nullptr;  // fp32 partial outputs of the attention's key splits: room for 4 * max_rows rows
   size_t attn_part_rows = 0;
+  float* smax_ml = nullptr;    // the softmax attention's key splits: running maximum and sum per (split, row, head)
+  int max_attn_heads = 0;
   // composite mixers, sandwich norms, routed feed-forwards
   bool sandwich = false;
   int max_rec_o = 0, max_rec_aux = 0, max_moe_top = 0, max_moe_experts = 0, max_moe_ff = 0;
@@ -54,7 +56,7 @@ size_t elem(const mtx_layered* e) { return e->cfg.float32 ? 4 : 2; }
 
 struct LWs {
   size_t x, y, qkv, v_shared, xa, q, attn, act, wanted, obf, attn_part, total;
-  size_t x0, rec_o, rec_aux, moe_logits, moe_weight, moe_y, moe_chosen, moe_slot, moe_row, moe_off, moe_act;
+  size_t smax_ml, x0, rec_o, rec_aux, moe_logits, moe_weight, moe_y, moe_chosen, moe_slot, moe_row, moe_off, moe_act;
 };
 
 LWs layered_layout(const mtx_layered* e) {
@@ -79,6 +81,7 @@ LWs layered_layout(const mtx_layered* e) {
   L.wanted = take(W * c.width * es);
   L.obf = take(R * size_t(e->max_nqkv > c.width ? e->max_nqkv : c.width) * 2);  // bf16 output of a tcgen05 projection
   L.attn_part = take(c.float32 ? 1024 : 4 * R * size_t(e->max_odim) * 4);
+  L.smax_ml = take(c.float32 ? 4 : 4 * R * size_t(e->max_attn_heads > 0 ? e->max_attn_heads : 1) * 2 * 4);
   L.x0 = take(e->sandwich ? R * c.width * 4 : 4);
   L.rec_o = take(R * size_t(e->max_rec_o > 0 ? e->max_rec_o : 1) * 4);
   L.rec_aux = take(R * size_t(e->max_rec_aux > 0 ? e->max_rec_aux : 1) * 4);
@@ -461,13 +464,23 @@ CompositeCols composite_cols(const mtx_layer_desc& l) {
   return cc;
 }
 
+template <int KIND, int CB>
+int launch_rec_scan_cb(const RecScanArgs& ra, int n_runs, cudaStream_t st) {
+  const dim3 grid(n_runs, ra.heads, (ra.vdim + CB - 1) / CB), block(CB * kRecSlices);
+  const size_t smem = rec_scan_smem_bytes(ra.dim, CB, ra.chunk);
+  const int rpt = rec_rpt(ra.dim);
+  if (rpt == 4) return launch(recurrent_scan_kernel<KIND, 4, CB>, grid, block, smem, st, ra);
+  if (rpt == 8) return launch(recurrent_scan_kernel<KIND, 8, CB>, grid, block, smem, st, ra);
+  if (rpt == 16) return launch(recurrent_scan_kernel<KIND, 16, CB>, grid, block, smem, st, ra);
+  return launch(recurrent_scan_kernel<KIND, 32, CB>, grid, block, smem, st, ra);
+}
+
+// 16 value columns per CTA when that still gives every SM two CTAs, else 8 (a walk is bound by latency: more CTAs, more overlap)
 template <int KIND>
-int launch_rec_scan(const RecScanArgs& ra, dim3 grid, size_t smem, cudaStream_t st) {
-  const int rpt = (ra.dim + kRecSlices - 1) / kRecSlices;
-  if (rpt <= 4) return launch(recurrent_scan_kernel<KIND, 4>, grid, dim3(kRecThreads), smem, st, ra);
-  if (rpt <= 8) return launch(recurrent_scan_kernel<KIND, 8>, grid, dim3(kRecThreads), smem, st, ra);
-  if (rpt <= 16) return launch(recurrent_scan_kernel<KIND, 16>, grid, dim3(kRecThreads), smem, st, ra);
-  return launch(recurrent_scan_kernel<KIND, 32>, grid, dim3(kRecThreads), smem, st, ra);
+int launch_rec_scan(mtx_layered* e, RecScanArgs& ra, int n_runs, cudaStream_t st) {
+  const bool wide = (long long)n_runs * ra.heads * ((ra.vdim + 15) / 16) >= 2LL * e->num_sms;
+  ra.chunk = rec_chunk_tokens(ra.dim, wide ? 16 : 8);
+  return wide ? launch_rec_scan_cb<KIND, 16>(ra, n_runs, st) : launch_rec_scan_cb<KIND, 8>(ra, n_runs, st);
 }
 
 // MTX_NORM_SANDWICH: x += wnorm(y + bias, post), then what comes before the next sublayer: the pre-adds of the next layer run
@@ -506,10 +519,32 @@ int launch_softmax_mma_t(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan& 
     MTX_CUDA(cudaFuncSetAttribute(softmax_attention_mma_kernel<D16, PARTS, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(plan.smem)));
     have = plan.smem;
   }
-  return launch(softmax_attention_mma_kernel<D16, PARTS, KT>, dim3(n_tiles, sa.kv_heads * plan.chunks), dim3(plan.warps * 32), plan.smem, st, sa, plan.chunks);
+  return launch(softmax_attention_mma_kernel<D16, PARTS, KT>, dim3(n_tiles, sa.kv_heads * plan.chunks, sa.splits), dim3(plan.warps * 32), plan.smem, st, sa,
+                plan.chunks);
 }
 
-int launch_softmax_mma(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan& plan, int n_tiles, cudaStream_t st) {
+int launch_softmax_mma_any(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan& plan, int n_tiles, cudaStream_t st);
+
+// a step of single tokens has few work items, each a long walk over its sequence's keys: the keys are cut into up to four splits
+// (the partial results' room) until every SM has about six CTAs, and a second kernel adds the parts
+int launch_softmax_mma(mtx_layered* e, SoftmaxAttnArgs<bf16> sa, const SoftmaxMmaPlan& plan, int n_tiles, bool single_rows, cudaStream_t st) {
+  sa.splits = 1;
+  const long long ctas = (long long)n_tiles * sa.kv_heads * plan.chunks;
+  if (single_rows && ctas < 3LL * e->num_sms) {
+    long long sp = (6LL * e->num_sms + ctas - 1) / ctas;
+    sa.splits = int(sp > 4 ? 4 : sp);
+    if (size_t(sa.splits) * sa.rows > e->attn_part_rows) sa.splits = 1;
+  }
+  if (sa.splits > 1) {
+    sa.part_o = e->attn_part;
+    sa.part_ml = e->smax_ml;
+  }
+  MTX_TRY(launch_softmax_mma_any(sa, plan, n_tiles, st));
+  if (sa.splits > 1) return launch(softmax_attention_merge_kernel, dim3((sa.rows * sa.heads + 3) / 4), dim3(128), 0, st, sa);
+  return MTX_OK;
+}
+
+int launch_softmax_mma_any(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan& plan, int n_tiles, cudaStream_t st) {
   switch (plan.d16) {
     case 1: return launch_softmax_mma_t<1, 1, 64>(sa, plan, n_tiles, st);
     case 2: return launch_softmax_mma_t<2, 1, 64>(sa, plan, n_tiles, st);
@@ -580,11 +615,13 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
     sa.max_pages = c.max_pages_per_group;
     sa.scale = a.scale;
     sa.out_scale = a.out_scale;
+    sa.splits = 1;
+    sa.rows = rows;
     bool done = false;
     if constexpr (sizeof(T) == 2) {
       const SoftmaxMmaPlan plan = softmax_mma_plan(a.heads, a.kv_heads, a.dim, a.vdim);
       if (plan.ok && use_softmax_mma() && cc.k_out % 2 == 0) {
-        MTX_TRY(launch_softmax_mma(sa, plan, b.n_tiles, st));
+        MTX_TRY(launch_softmax_mma(e, sa, plan, b.n_tiles, b.n_tiles == rows, st));
         done = true;
       }
     }
@@ -632,13 +669,10 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
     ra.heads = r.heads;
     ra.dim = r.dim;
     ra.vdim = r.vdim;
-    ra.chunk = rec_chunk_tokens(r.dim);
     ra.q_scale = r.q_scale;
     ra.denom_eps = r.denom_eps;
-    const dim3 grid(b.n_runs, r.heads, (r.vdim + kRecCols - 1) / kRecCols);
-    const size_t smem = rec_scan_smem_bytes(r.dim, ra.chunk);
-    if (r.kind == MTX_REC_GLA) MTX_TRY(launch_rec_scan<REC_GLA>(ra, grid, smem, st));
-    else MTX_TRY(launch_rec_scan<REC_MLSTM>(ra, grid, smem, st));
+    if (r.kind == MTX_REC_GLA) MTX_TRY(launch_rec_scan<REC_GLA>(e, ra, b.n_runs, st));
+    else MTX_TRY(launch_rec_scan<REC_MLSTM>(e, ra, b.n_runs, st));
     RecOutArgs<T> oa;
     memset(&oa, 0, sizeof(oa));
     oa.o = e->rec_o;
@@ -738,6 +772,7 @@ int check_composite(mtx_layered* e, int i) {
     if (kSmaxRows * a.vdim > kSmaxThreads * kSmaxMaxAcc) return fail(MTX_ERR_UNSUPPORTED, "layer %d: vdim %d exceeds %d", i, a.vdim, kSmaxThreads * kSmaxMaxAcc / kSmaxRows);
     if (softmax_attn_smem_bytes(a.dim, a.vdim) > 200 * 1024) return fail(MTX_ERR_UNSUPPORTED, "layer %d: the attention's heads do not fit shared memory", i);
     if (a.heads * a.dim > e->max_qdim) e->max_qdim = a.heads * a.dim;
+    if (a.heads > e->max_attn_heads) e->max_attn_heads = a.heads;
   }
   if (r.kind != 0) {
     if (r.kind != MTX_REC_GLA && r.kind != MTX_REC_MLSTM) return fail(MTX_ERR_UNSUPPORTED, "layer %d: unknown recurrence %d", i, r.kind);
@@ -879,6 +914,7 @@ int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes) {
   e->obf = base + L.obf;
   e->attn_part = reinterpret_cast<float*>(base + L.attn_part);
   e->attn_part_rows = 4 * align_up(size_t(e->cfg.max_rows), 256);
+  e->smax_ml = reinterpret_cast<float*>(base + L.smax_ml);
   e->x0 = reinterpret_cast<float*>(base + L.x0);
   e->rec_o = reinterpret_cast<float*>(base + L.rec_o);
   e->rec_aux = reinterpret_cast<float*>(base + L.rec_aux);

@@ -95,30 +95,38 @@ __device__ __forceinline__ void lin_store_pair(const LinArgs<T>& p, int r, int c
   if (c + 1 < p.n) o[1] = v1;
 }
 
-// ---- bf16: 64 x 64 x 32 tiles, four warps of 32 x 32 ---------------------------------------------------------------------
+// ---- bf16: 64 x 64 x 64 tiles, four warps of 32 x 32 ---------------------------------------------------------------------
 constexpr int kLinThreads = 128;
-constexpr int kLinBM = 64, kLinBN = 64, kLinBK = 32, kLinPitch = kLinBK + 8;  // 80-byte rows: fragment reads hit 32 banks
+constexpr int kLinBM = 64, kLinBN = 64, kLinBK = 64, kLinPitch = kLinBK + 8;  // 144-byte rows: fragment reads hit 32 banks
 
-__device__ __forceinline__ void lin_load_tile(const bf16* src, long long ld, int row0, int n_rows, int k0, int k, bool vec, bf16* dst, int tid,
-                                              const int* row_map = nullptr) {
-  // 64 rows x 32 columns: 256 chunks of 8 elements, two per thread
+// 64 rows x 64 columns of an operand: 512 chunks of 8 elements, four per thread; fetched into registers one k step ahead of their
+// use (the loads of step k + 1 are in flight while step k's tensor-core work runs), then stored to shared memory
+__device__ __forceinline__ void lin_fetch_tile(const bf16* src, long long ld, int row0, int n_rows, int k0, int k, bool vec, uint4 (&v)[4], int tid,
+                                               const int* row_map = nullptr) {
 #pragma unroll
-  for (int it = 0; it < 2; ++it) {
-    const int chunk = tid + it * kLinThreads, r = chunk >> 2, c = (chunk & 3) * 8;
+  for (int it = 0; it < 4; ++it) {
+    const int chunk = tid + it * kLinThreads, r = chunk >> 3, c = (chunk & 7) * 8;
     const int gr = row0 + r, gc = k0 + c;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (gr < n_rows) {
+    v[it] = make_uint4(0u, 0u, 0u, 0u);
+    if (gr < n_rows && gc < k) {
       const bf16* s = src + size_t(row_map ? row_map[gr] : gr) * ld + gc;
       if (vec && gc + 8 <= k) {
-        v = *reinterpret_cast<const uint4*>(s);
+        v[it] = *reinterpret_cast<const uint4*>(s);
       } else {
         bf16 tmp[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) tmp[e] = (gc + e < k) ? s[e] : __float2bfloat16_rn(0.0f);
-        v = *reinterpret_cast<const uint4*>(tmp);
+        v[it] = *reinterpret_cast<const uint4*>(tmp);
       }
     }
-    *reinterpret_cast<uint4*>(dst + r * kLinPitch + c) = v;
+  }
+}
+
+__device__ __forceinline__ void lin_store_tile(const uint4 (&v)[4], bf16* dst, int tid) {
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int chunk = tid + it * kLinThreads, r = chunk >> 3, c = (chunk & 7) * 8;
+    *reinterpret_cast<uint4*>(dst + r * kLinPitch + c) = v[it];
   }
 }
 
@@ -141,10 +149,17 @@ __global__ void __launch_bounds__(kLinThreads) linear_mma_kernel(const LinArgs<b
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
+  uint4 ra[4], rb[4];
+  lin_fetch_tile(p.a, p.lda, row0, p.rows, 0, p.k, vec_a, ra, tid, p.a_row);
+  lin_fetch_tile(p.w, p.k, col0, p.n, 0, p.k, vec_w, rb, tid);
   for (int k0 = 0; k0 < p.k; k0 += kLinBK) {
-    lin_load_tile(p.a, p.lda, row0, p.rows, k0, p.k, vec_a, sa, tid, p.a_row);
-    lin_load_tile(p.w, p.k, col0, p.n, k0, p.k, vec_w, sb, tid);
+    lin_store_tile(ra, sa, tid);
+    lin_store_tile(rb, sb, tid);
     __syncthreads();
+    if (k0 + kLinBK < p.k) {
+      lin_fetch_tile(p.a, p.lda, row0, p.rows, k0 + kLinBK, p.k, vec_a, ra, tid, p.a_row);
+      lin_fetch_tile(p.w, p.k, col0, p.n, k0 + kLinBK, p.k, vec_w, rb, tid);
+    }
 #pragma unroll
     for (int kk = 0; kk < kLinBK; kk += 16) {
       uint32_t af[2][4], bfr[4][2];

@@ -9,8 +9,8 @@
 // A run (consecutive rows of one sequence) is walked in order from the group's state; a run that starts at position 0 starts
 // from zero instead, so a slot that is handed to another sequence needs no clearing.  Every value column of S is independent of
 // the others, so a (run, head) is spread over CTAs by column block: a CTA keeps its columns of S in registers (8 row slices x
-// 16 columns), stages the run's q / k / decays / v in chunks through shared memory and walks the tokens one by one.  The result
-// of a token is the same bits however the sequence is cut into steps.
+// 8 or 16 columns), stages the run's q / k / decays / v in chunks through shared memory (cp.async, two stages) and walks the
+// tokens in order.  The result of a token is the same bits however the sequence is cut into steps.
 //
 //   recurrent_prepare_kernel   per row: the GLA's decays (low-rank up-projection, bias, sigmoid^(1/tau)) or the mLSTM's two log gates
 //   recurrent_scan_kernel      the walk
@@ -69,7 +69,7 @@ struct RecScanArgs {
   int q_col, k_col, v_col;
   const float* aux;    // the prepare kernel's output
   float* o;            // [rows, heads * vdim]
-  float* state_s;      // [slots, heads, dim, vdim]
+  float* state_s;      // [slots, heads, vdim, dim]: a value column's dim entries are contiguous
   float* state_n;      // mLSTM [slots, heads, dim]
   float* state_m;      // mLSTM [slots, heads]
   const int* run_row0; // [n_runs + 1]
@@ -79,127 +79,232 @@ struct RecScanArgs {
   float q_scale, denom_eps;
 };
 
-constexpr int kRecThreads = 128, kRecCols = 16, kRecSlices = 8;
+// A CTA owns CB value columns of one (run, head): thread (column jl, slice sl) keeps RPT key channels of its column of S in
+// registers, in groups of four: channels g * 32 + sl * 4 .. + 3 for g < RPT / 4 (8 slices: dim <= 8 * RPT), so that the eight
+// slices of a column read 128 contiguous bytes of the state and of the staged q / k / decays at a time.  The run's q / k / decays (or gates)
+// / v arrive in chunks of `chunk` tokens (a multiple of 4) through a two-stage cp.async ring; tokens are walked four at a time
+// so that the four read-outs' reductions overlap (the state update itself is the only chain from token to token).
+constexpr int kRecSlices = 8, kRecUnroll = 4;
 
-inline int rec_chunk_tokens(int dim) {
-  int t = (40 * 1024) / int(sizeof(float) * (3 * dim + kRecCols + 2));
-  return t > 16 ? 16 : (t < 1 ? 1 : t);
+// floats of one token in a stage: q, k, decays (8 * RPT channels each), then CB values, then 4 scalars (mLSTM: log input gate,
+// log forget gate; later keep, put, floor)
+__host__ __device__ inline int rec_token_floats(int rpt, int cb) { return 3 * kRecSlices * rpt + cb + 4; }
+inline int rec_rpt(int dim) {
+  const int r = (dim + kRecSlices - 1) / kRecSlices;
+  return r <= 4 ? 4 : (r <= 8 ? 8 : (r <= 16 ? 16 : 32));
 }
-inline size_t rec_scan_smem_bytes(int dim, int chunk) { return sizeof(float) * size_t(chunk) * (3 * dim + kRecCols + 2); }
+inline int rec_chunk_tokens(int dim, int cb) {
+  int t = (48 * 1024) / int(sizeof(float) * 2 * rec_token_floats(rec_rpt(dim), cb));
+  t = t / kRecUnroll * kRecUnroll;
+  return t > 32 ? 32 : (t < kRecUnroll ? kRecUnroll : t);
+}
+inline size_t rec_scan_smem_bytes(int dim, int cb, int chunk) { return sizeof(float) * 2 * size_t(chunk) * rec_token_floats(rec_rpt(dim), cb); }
 
-template <int KIND, int RPT>
-__global__ void __launch_bounds__(kRecThreads) recurrent_scan_kernel(const RecScanArgs a) {
-  extern __shared__ float smem[];
+__device__ __forceinline__ void rec_cp_async_4(float* dst, const float* src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int KIND, int RPT, int CB>
+__global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const RecScanArgs a) {
+  extern __shared__ __align__(16) float rec_smem[];
+  constexpr int NT = CB * kRecSlices, QP = kRecSlices * RPT, TF = 3 * QP + CB + 4, GS = 4 * kRecSlices;  // GS: channels per group of float4s
   const int d = a.dim, dv = a.vdim, H = a.heads, TC = a.chunk;
-  float* sq = smem;            // [TC][d]
-  float* sk = sq + TC * d;     // [TC][d]
-  float* sa = sk + TC * d;     // [TC][d] decays (GLA)
-  float* sv = sa + TC * d;     // [TC][16]
-  float* sg = sv + TC * kRecCols;  // [TC][2] log gates (mLSTM)
-  const int tid = threadIdx.x, jl = tid >> 3, sl = tid & 7;
+  const int tid = threadIdx.x, jl = tid / kRecSlices, sl = tid % kRecSlices;
   griddep_wait();
   const int r0 = a.run_row0[blockIdx.x], nr = a.run_row0[blockIdx.x + 1] - r0, h = blockIdx.y;
   if (nr <= 0) return;
-  const int col0 = blockIdx.z * kRecCols, j = col0 + jl;
+  const int col0 = blockIdx.z * CB, j = col0 + jl;
   const bool col_ok = j < dv;
   const int slot = a.group[r0];
   const bool fresh = a.pos[r0] == 0;
+  auto channel = [&](int i) { return (i >> 2) * GS + sl * 4 + (i & 3); };  // this thread's i-th key channel
+  const bool vec = (d & 3) == 0;  // whole float4s of the state
   float S[RPT], N[RPT];
-  float m = 0.0f;
-  float* gs = a.state_s + (size_t(slot) * H + h) * d * dv;
+  float* gs = a.state_s + ((size_t(slot) * H + h) * dv + (col_ok ? j : 0)) * d;
+  float* gn = a.state_n + (size_t(slot) * H + h) * d;
 #pragma unroll
-  for (int i = 0; i < RPT; ++i) {
-    const int r = sl + kRecSlices * i;
-    S[i] = (!fresh && col_ok && r < d) ? gs[size_t(r) * dv + j] : 0.0f;
-    N[i] = 0.0f;
-  }
-  if (KIND == REC_MLSTM && !fresh) {
+  for (int i = 0; i < RPT; ++i) S[i] = N[i] = 0.0f;
+  float m = 0.0f;  // (thread 0 walks the running maximum)
+  if (!fresh) {
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) {
-      const int r = sl + kRecSlices * i;
-      if (r < d) N[i] = a.state_n[(size_t(slot) * H + h) * d + r];
-    }
-    m = a.state_m[size_t(slot) * H + h];
-  }
-  for (int t0 = 0; t0 < nr; t0 += TC) {
-    const int nt = nr - t0 < TC ? nr - t0 : TC;
-    __syncthreads();
-    for (int e = tid; e < nt * d; e += kRecThreads) {
-      const int t = e / d, c = e % d;
-      const float* row = a.proj + size_t(r0 + t0 + t) * a.ld;
-      sq[e] = row[a.q_col + h * d + c] * a.q_scale;
-      sk[e] = row[a.k_col + h * d + c];
-      if (KIND == REC_GLA) sa[e] = a.aux[size_t(r0 + t0 + t) * H * d + h * d + c];
-    }
-    for (int e = tid; e < nt * kRecCols; e += kRecThreads) {
-      const int t = e / kRecCols, c = e % kRecCols;
-      sv[e] = col0 + c < dv ? a.proj[size_t(r0 + t0 + t) * a.ld + a.v_col + h * dv + col0 + c] : 0.0f;
-    }
-    if (KIND == REC_MLSTM) {
-      for (int e = tid; e < nt * 2; e += kRecThreads) {
-        const int t = e >> 1, w = e & 1;
-        sg[e] = a.aux[size_t(r0 + t0 + t) * 2 * H + w * H + h];
-      }
-    }
-    __syncthreads();
-    for (int t = 0; t < nt; ++t) {
-      const float* q = sq + t * d;
-      const float* k = sk + t * d;
-      const float v = sv[t * kRecCols + jl];
-      float part = 0.0f, npart = 0.0f, floor_m = 0.0f;
-      if (KIND == REC_GLA) {
-        const float* al = sa + t * d;
-#pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-          const int r = sl + kRecSlices * i;
-          if (r < d) {
-            S[i] = fmaf(al[r], S[i], k[r] * v);
-            part = fmaf(S[i], q[r], part);
-          }
+    for (int i4 = 0; i4 < RPT; i4 += 4) {
+      const int r = channel(i4);
+      if (vec) {
+        if (r < d && col_ok) {
+          const float4 v4 = *reinterpret_cast<const float4*>(gs + r);
+          S[i4] = v4.x, S[i4 + 1] = v4.y, S[i4 + 2] = v4.z, S[i4 + 3] = v4.w;
+        }
+        if (KIND == REC_MLSTM && r < d) {
+          const float4 v4 = *reinterpret_cast<const float4*>(gn + r);
+          N[i4] = v4.x, N[i4 + 1] = v4.y, N[i4 + 2] = v4.z, N[i4 + 3] = v4.w;
         }
       } else {
-        const float ig = sg[2 * t], fg = sg[2 * t + 1];
-        const float m_new = fmaxf(fg + m, ig);
-        const float keep = expf(fg + m - m_new), put = expf(ig - m_new);
-        m = m_new;
-        floor_m = expf(-m_new);
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-          const int r = sl + kRecSlices * i;
-          if (r < d) {
-            const float pk = put * k[r];
-            S[i] = fmaf(keep, S[i], pk * v);
-            N[i] = fmaf(keep, N[i], pk);
-            part = fmaf(S[i], q[r], part);
-            npart = fmaf(N[i], q[r], npart);
+        for (int e = 0; e < 4; ++e) {
+          if (r + e < d && col_ok) S[i4 + e] = gs[r + e];
+          if (KIND == REC_MLSTM && r + e < d) N[i4 + e] = gn[r + e];
+        }
+      }
+    }
+    if (KIND == REC_MLSTM) m = a.state_m[size_t(slot) * H + h];
+  }
+  const int n_chunks = (nr + TC - 1) / TC;
+
+  // stage <- chunk c: every element by a 4-byte cp.async (the projection's columns have no alignment to count on); the tail of
+  // the last chunk and the key channels beyond dim are filled with values that leave the state alone (k = v = q = 0, decay 1)
+  auto load_chunk = [&](int c, int stage) {
+    float* base = rec_smem + size_t(stage) * TC * TF;
+    const int t0 = c * TC;
+    const int slots_d = kRecSlices * RPT;  // padded key channels
+    const int left = (nr - t0 + kRecUnroll - 1) / kRecUnroll * kRecUnroll, TL = left < TC ? left : TC;  // tokens the walk will touch
+    for (int e = tid; e < TL * slots_d; e += NT) {
+      const int t = e / slots_d, r = e % slots_d;
+      float* dst = base + t * TF + r;
+      const bool ok = t0 + t < nr && r < d;
+      const float* row = a.proj + size_t(r0 + t0 + t) * a.ld;
+      if (ok) {
+        rec_cp_async_4(dst, row + a.q_col + h * d + r);
+        rec_cp_async_4(dst + QP, row + a.k_col + h * d + r);
+        if (KIND == REC_GLA) rec_cp_async_4(dst + 2 * QP, a.aux + size_t(r0 + t0 + t) * H * d + h * d + r);
+      } else {
+        dst[0] = 0.0f;
+        dst[QP] = 0.0f;
+        if (KIND == REC_GLA) dst[2 * QP] = 1.0f;
+      }
+    }
+    for (int e = tid; e < TL * CB; e += NT) {
+      const int t = e / CB, c2 = e % CB;
+      float* dst = base + t * TF + 3 * QP + c2;
+      if (t0 + t < nr && col0 + c2 < dv) rec_cp_async_4(dst, a.proj + size_t(r0 + t0 + t) * a.ld + a.v_col + h * dv + col0 + c2);
+      else dst[0] = 0.0f;
+    }
+    if (KIND == REC_MLSTM) {
+      for (int e = tid; e < TL * 2; e += NT) {
+        const int t = e >> 1, w = e & 1;
+        float* dst = base + t * TF + 3 * QP + CB + w;
+        if (t0 + t < nr) rec_cp_async_4(dst, a.aux + size_t(r0 + t0 + t) * 2 * H + w * H + h);
+        else dst[0] = w ? 0.0f : -INFINITY;  // (forget gate 0, input gate -inf: keep = 1, put = 0)
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  load_chunk(0, 0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) {
+      load_chunk(c + 1, (c + 1) & 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    float* base = rec_smem + size_t(c & 1) * TC * TF;
+    const int t0 = c * TC;
+    const int left = (nr - t0 + kRecUnroll - 1) / kRecUnroll * kRecUnroll, TL = left < TC ? left : TC;
+    if (KIND == REC_MLSTM) {
+      // the running maximum is a chain over the tokens: one thread walks it, then the factors of all tokens at once
+      float* sc = base + 3 * QP + CB;  // [t * TF + 0..3]: i, f -> keep, put, floor; [3] = m before the token
+      if (tid == 0) {
+        for (int t = 0; t < TL; ++t) {
+          sc[t * TF + 3] = m;
+          m = fmaxf(sc[t * TF + 1] + m, sc[t * TF]);
+          sc[t * TF + 2] = m;
+        }
+      }
+      __syncthreads();
+      if (tid < TL) {
+        float* q = sc + tid * TF;
+        const float ig = q[0], fg = q[1], m_new = q[2], m_old = q[3];
+        q[0] = expf(fg + m_old - m_new);
+        q[1] = expf(ig - m_new);
+        q[2] = expf(-m_new);
+      }
+      __syncthreads();
+    }
+    for (int t = 0; t < TL; t += kRecUnroll) {
+      float part[kRecUnroll], npart[kRecUnroll], floor_m[kRecUnroll];
+#pragma unroll
+      for (int u = 0; u < kRecUnroll; ++u) {
+        const float* tok = base + (t + u) * TF;
+        const float* q = tok + sl * 4;
+        const float* k = q + QP;
+        const float v = tok[3 * QP + jl];
+        part[u] = 0.0f;
+        npart[u] = 0.0f;
+        floor_m[u] = 0.0f;
+        if (KIND == REC_GLA) {
+          const float* al = k + QP;
+#pragma unroll
+          for (int i4 = 0; i4 < RPT; i4 += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * kRecSlices), q4 = *reinterpret_cast<const float4*>(q + i4 * kRecSlices),
+                         a4 = *reinterpret_cast<const float4*>(al + i4 * kRecSlices);
+            S[i4] = fmaf(a4.x, S[i4], k4.x * v);
+            S[i4 + 1] = fmaf(a4.y, S[i4 + 1], k4.y * v);
+            S[i4 + 2] = fmaf(a4.z, S[i4 + 2], k4.z * v);
+            S[i4 + 3] = fmaf(a4.w, S[i4 + 3], k4.w * v);
+            part[u] = fmaf(S[i4], q4.x, part[u]);
+            part[u] = fmaf(S[i4 + 1], q4.y, part[u]);
+            part[u] = fmaf(S[i4 + 2], q4.z, part[u]);
+            part[u] = fmaf(S[i4 + 3], q4.w, part[u]);
+          }
+        } else {
+          const float keep = tok[3 * QP + CB], put = tok[3 * QP + CB + 1];
+          floor_m[u] = tok[3 * QP + CB + 2];
+#pragma unroll
+          for (int i4 = 0; i4 < RPT; i4 += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * kRecSlices), q4 = *reinterpret_cast<const float4*>(q + i4 * kRecSlices);
+            const float pk[4] = {put * k4.x, put * k4.y, put * k4.z, put * k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              S[i4 + e] = fmaf(keep, S[i4 + e], pk[e] * v);
+              N[i4 + e] = fmaf(keep, N[i4 + e], pk[e]);
+              part[u] = fmaf(S[i4 + e], qq[e], part[u]);
+              npart[u] = fmaf(N[i4 + e], qq[e], npart[u]);
+            }
           }
         }
       }
 #pragma unroll
       for (int o = 1; o < kRecSlices; o <<= 1) {
-        part += __shfl_xor_sync(0xffffffffu, part, o);
-        if (KIND == REC_MLSTM) npart += __shfl_xor_sync(0xffffffffu, npart, o);
+#pragma unroll
+        for (int u = 0; u < kRecUnroll; ++u) {
+          part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
+          if (KIND == REC_MLSTM) npart[u] += __shfl_xor_sync(0xffffffffu, npart[u], o);
+        }
       }
-      if (sl == 0 && col_ok) {
-        float out = part;
-        if (KIND == REC_MLSTM) out = part / (fmaxf(fabsf(npart), floor_m) + a.denom_eps);
-        a.o[size_t(r0 + t0 + t) * H * dv + h * dv + j] = out;
+      if (sl < kRecUnroll && col_ok && t0 + t + sl < nr) {  // slice u writes token t + u
+        float out = 0.0f, nq = 0.0f, fl = 0.0f;
+#pragma unroll
+        for (int u = 0; u < kRecUnroll; ++u)
+          if (sl == u) {
+            out = part[u];
+            nq = npart[u];
+            fl = floor_m[u];
+          }
+        out *= a.q_scale;
+        if (KIND == REC_MLSTM) out = out / (fmaxf(fabsf(nq * a.q_scale), fl) + a.denom_eps);
+        a.o[size_t(r0 + t0 + t + sl) * H * dv + h * dv + j] = out;
+      }
+    }
+    __syncthreads();  // the stage is free for the chunk after next
+  }
+  const bool write_n = KIND == REC_MLSTM && blockIdx.z == 0 && jl == 0;
+#pragma unroll
+  for (int i4 = 0; i4 < RPT; i4 += 4) {
+    const int r = channel(i4);
+    if (vec) {
+      if (r < d && col_ok) *reinterpret_cast<float4*>(gs + r) = make_float4(S[i4], S[i4 + 1], S[i4 + 2], S[i4 + 3]);
+      if (write_n && r < d) *reinterpret_cast<float4*>(gn + r) = make_float4(N[i4], N[i4 + 1], N[i4 + 2], N[i4 + 3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (r + e < d && col_ok) gs[r + e] = S[i4 + e];
+        if (write_n && r + e < d) gn[r + e] = N[i4 + e];
       }
     }
   }
-#pragma unroll
-  for (int i = 0; i < RPT; ++i) {
-    const int r = sl + kRecSlices * i;
-    if (col_ok && r < d) gs[size_t(r) * dv + j] = S[i];
-  }
-  if (KIND == REC_MLSTM && blockIdx.z == 0 && jl == 0) {
-#pragma unroll
-    for (int i = 0; i < RPT; ++i) {
-      const int r = sl + kRecSlices * i;
-      if (r < d) a.state_n[(size_t(slot) * H + h) * d + r] = N[i];
-    }
-    if (sl == 0) a.state_m[size_t(slot) * H + h] = m;
-  }
+  if (write_n && tid == 0) a.state_m[size_t(slot) * H + h] = m;
 }
 
 template <typename T>

@@ -102,6 +102,11 @@ struct SoftmaxAttnArgs {
   int heads, kv_heads, dim, vdim, window;
   int num_pages, tokens_per_page, max_pages;
   float scale, out_scale;
+  // key splits of the tensor-core arm (splits > 1: blockIdx.z walks every splits-th part of the key tiles and leaves an
+  // unnormalised partial result; softmax_attention_merge_kernel adds the parts)
+  int splits, rows;
+  float* part_o;   // [splits, rows, H, dv]
+  float* part_ml;  // [splits, rows, H, 2]: running maximum, sum
 };
 
 constexpr int kSmaxThreads = 256, kSmaxRows = 16, kSmaxKeys = 32;
@@ -253,7 +258,15 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
   if (a.window > 0 && p0 - a.window + 1 > 0) lo = p0 - a.window + 1;
   const int* pages = a.page_map + size_t(grp) * a.max_pages;
   const size_t head_rows = size_t(kvh) * a.num_pages * a.tokens_per_page;
-  const int n_key_tiles = (p_last - lo) / KT + 1;
+  const int all_key_tiles = (p_last - lo) / KT + 1;
+  int tile_lo = 0, n_key_tiles = all_key_tiles;
+  if (a.splits > 1) {
+    const int per = (all_key_tiles + a.splits - 1) / a.splits;
+    tile_lo = int(blockIdx.z) * per;
+    n_key_tiles = all_key_tiles - tile_lo < per ? all_key_tiles - tile_lo : per;
+    if (n_key_tiles < 0) n_key_tiles = 0;
+    lo += tile_lo * KT;
+  }
 
   auto load_tile = [&](int it, int stage) {
     bf16* sk = stage0 + size_t(stage) * 2 * KT * PITCH;
@@ -292,7 +305,7 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   const int pi0 = p0 + g, pi1 = p0 + g + 8;
 
-  load_tile(0, 0);
+  if (n_key_tiles > 0) load_tile(0, 0);
   for (int it = 0; it < n_key_tiles; ++it) {
     if (it + 1 < n_key_tiles) {
       load_tile(it + 1, (it + 1) & 1);
@@ -383,6 +396,24 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
+  if (a.splits > 1) {
+    const size_t base0 = (size_t(blockIdx.z) * a.rows + r0 + g) * a.heads + h, base1 = base0 + size_t(8) * a.heads;
+    if (g < nr && t == 0 && part == 0) {
+      a.part_ml[base0 * 2] = m_run[0];
+      a.part_ml[base0 * 2 + 1] = l_run[0];
+    }
+    if (g + 8 < nr && t == 0 && part == 0) {
+      a.part_ml[base1 * 2] = m_run[1];
+      a.part_ml[base1 * 2 + 1] = l_run[1];
+    }
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      const int col = part * DVW + nb * 8 + 2 * t;
+      if (g < nr) *reinterpret_cast<float2*>(a.part_o + base0 * D + col) = make_float2(o[nb][0], o[nb][1]);
+      if (g + 8 < nr) *reinterpret_cast<float2*>(a.part_o + base1 * D + col) = make_float2(o[nb][2], o[nb][3]);
+    }
+    return;
+  }
   const float f0 = a.out_scale / l_run[0], f1 = a.out_scale / l_run[1];
   bf16* out0 = a.out + size_t(r0 + g) * a.ld_out + h * D + part * DVW + 2 * t;
   bf16* out1 = out0 + size_t(8) * a.ld_out;
@@ -390,6 +421,30 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
   for (int nb = 0; nb < NB; ++nb) {
     if (g < nr) *reinterpret_cast<uint32_t*>(out0 + nb * 8) = smax_pack_bf16(o[nb][0] * f0, o[nb][1] * f0);
     if (g + 8 < nr) *reinterpret_cast<uint32_t*>(out1 + nb * 8) = smax_pack_bf16(o[nb][2] * f1, o[nb][3] * f1);
+  }
+}
+
+// out[row, h] = out_scale * sum_z e^(m_z - M) o_z / sum_z e^(m_z - M) l_z, M = max_z m_z; one warp per (row, head)
+__global__ void __launch_bounds__(128) softmax_attention_merge_kernel(const SoftmaxAttnArgs<bf16> a) {
+  griddep_wait();
+  const int unit = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (unit >= a.rows * a.heads) return;
+  const int row = unit / a.heads, h = unit % a.heads, D = a.vdim;
+  float M = -INFINITY;
+  for (int z = 0; z < a.splits; ++z) M = fmaxf(M, a.part_ml[((size_t(z) * a.rows + row) * a.heads + h) * 2]);
+  float L = 0.0f;
+  for (int z = 0; z < a.splits; ++z) {
+    const float* ml = a.part_ml + ((size_t(z) * a.rows + row) * a.heads + h) * 2;
+    if (ml[0] != -INFINITY) L += __expf(ml[0] - M) * ml[1];
+  }
+  for (int c = lane; c < D; c += 32) {
+    float acc = 0.0f;
+    for (int z = 0; z < a.splits; ++z) {
+      const size_t base = (size_t(z) * a.rows + row) * a.heads + h;
+      const float mz = a.part_ml[base * 2];
+      if (mz != -INFINITY) acc = fmaf(__expf(mz - M), a.part_o[base * D + c], acc);
+    }
+    a.out[size_t(row) * a.ld_out + h * D + c] = __float2bfloat16_rn(acc * a.out_scale / L);
   }
 }
 

@@ -243,7 +243,7 @@ class LayeredEngine(MaxEngine):
             setattr(d.rec, k, ptr(r.get(k)))
           H, dk, dv = int(r["heads"]), int(r["dim"]), int(r["vdim"])
           f32 = torch.float32
-          states = (torch.zeros(slots, H, dk, dv, dtype=f32, device=dev),)
+          states = (torch.zeros(slots, H, dv, dk, dtype=f32, device=dev),)
           d.rec.state_s = states[0].data_ptr()
           if r["kind"] == "mlstm":
             states += (torch.zeros(slots, H, dk, dtype=f32, device=dev), torch.zeros(slots, H, dtype=f32, device=dev))
@@ -462,6 +462,34 @@ class LayeredEngine(MaxEngine):
     self._active[slot].fill_(1)
     self._logits[slot].copy_(prefix["logits"][0])
     return decode_state
+
+  def fill_synthetic_context(self, prefill_lengths, ar_lengths=None, seed: int = 7) -> dict:
+    """Benchmark set-up (as MaxEngine.fill_synthetic_context): every slot holds a context of the given length without a prefill
+    having run -- its pages are reserved, the pools hold random-normal rows, the recurrent states small random numbers."""
+    B = self.max_concurrent_decodes
+    state = self.init_decode_state()
+    g = torch.Generator(device=self.device).manual_seed(seed)
+    ps = self.page_state
+    for slot in range(B):
+      n = int(prefill_lengths[slot]) + (int(ar_lengths[slot]) if ar_lengths is not None else 0)
+      ps = self.page_manager.extend_pages(ps, slot, n)
+      if int(ps.sequence_lengths[slot]) != n:
+        raise ValueError("pagedattn_num_pages is too small for the synthetic contexts")
+      self._next_pos[slot].fill_(n)
+    self.page_state = ps
+    self._upload_page_map()
+    for pool in self._pools:
+      for buf in pool:
+        flat = buf.view(-1)
+        for lo in range(0, flat.numel(), 1 << 26):
+          n = min(1 << 26, flat.numel() - lo)
+          flat[lo : lo + n] = torch.randn(n, device=self.device, generator=g).to(buf.dtype)
+    for st in self._states:
+      for t in st:
+        t.copy_(torch.randn(t.shape, device=self.device, generator=g) * 0.1)
+    self._active.fill_(1)
+    self._tokens.copy_(torch.randint(0, int(self.config.vocab_size), self._tokens.shape, device=self.device, generator=g, dtype=torch.int32))
+    return state
 
   def bulk_insert(self, prefix: dict, decode_state: dict, slots: list) -> dict:
     raise NotImplementedError("a paged prefix belongs to one slot")
