@@ -525,6 +525,41 @@ int launch_softmax_mma_t(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan& 
 
 int launch_softmax_mma_any(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan& plan, int n_tiles, cudaStream_t st);
 
+template <int D16>
+int launch_softmax_decode_t(const SoftmaxAttnArgs<bf16>& sa, cudaStream_t st) {
+  const size_t smem = softmax_decode_smem_bytes(sa.dim);
+  static size_t have = 0;  // per instantiation
+  if (smem > 48 * 1024 && smem > have) {
+    MTX_CUDA(cudaFuncSetAttribute(softmax_attention_decode_kernel<D16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    have = smem;
+  }
+  return launch(softmax_attention_decode_kernel<D16>, dim3(sa.rows, sa.kv_heads, sa.splits), dim3(kSdecWarps * 32), smem, st, sa);
+}
+
+// a step of single tokens (every row its own tile and sequence): the transposed kernel, its keys cut into splits until every SM
+// has about three CTAs (what its shared memory lets an SM hold)
+int launch_softmax_decode(mtx_layered* e, SoftmaxAttnArgs<bf16> sa, int d16, cudaStream_t st) {
+  const long long ctas = (long long)sa.rows * sa.kv_heads;
+  long long sp = (3LL * e->num_sms + ctas - 1) / ctas;
+  sa.splits = int(sp > 4 ? 4 : (sp < 1 ? 1 : sp));
+  if (size_t(sa.splits) * sa.rows > e->attn_part_rows) sa.splits = 1;
+  sa.part_o = e->attn_part;
+  sa.part_ml = e->smax_ml;
+  int rc = MTX_ERR_UNSUPPORTED;
+  switch (d16) {
+    case 1: rc = launch_softmax_decode_t<1>(sa, st); break;
+    case 2: rc = launch_softmax_decode_t<2>(sa, st); break;
+    case 3: rc = launch_softmax_decode_t<3>(sa, st); break;
+    case 4: rc = launch_softmax_decode_t<4>(sa, st); break;
+    case 6: rc = launch_softmax_decode_t<6>(sa, st); break;
+    case 8: rc = launch_softmax_decode_t<8>(sa, st); break;
+    case 16: rc = launch_softmax_decode_t<16>(sa, st); break;
+  }
+  MTX_TRY(rc);
+  if (sa.splits > 1) return launch(softmax_attention_merge_kernel, dim3((sa.rows * sa.heads + 3) / 4), dim3(128), 0, st, sa);
+  return MTX_OK;
+}
+
 // a step of single tokens has few work items, each a long walk over its sequence's keys: the keys are cut into up to four splits
 // (the partial results' room) until every SM has about six CTAs, and a second kernel adds the parts
 int launch_softmax_mma(mtx_layered* e, SoftmaxAttnArgs<bf16> sa, const SoftmaxMmaPlan& plan, int n_tiles, bool single_rows, cudaStream_t st) {
@@ -620,8 +655,10 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
     bool done = false;
     if constexpr (sizeof(T) == 2) {
       const SoftmaxMmaPlan plan = softmax_mma_plan(a.heads, a.kv_heads, a.dim, a.vdim);
+      static const int decode_arm = env_int("MTX_SOFTMAX_DECODE", 1);
       if (plan.ok && use_softmax_mma() && cc.k_out % 2 == 0) {
-        MTX_TRY(launch_softmax_mma(e, sa, plan, b.n_tiles, b.n_tiles == rows, st));
+        if (b.n_tiles == rows && a.heads / a.kv_heads <= 8 && decode_arm) MTX_TRY(launch_softmax_decode(e, sa, plan.d16, st));
+        else MTX_TRY(launch_softmax_mma(e, sa, plan, b.n_tiles, b.n_tiles == rows, st));
         done = true;
       }
     }

@@ -18,6 +18,12 @@
 //                              value columns); S = Q K^T and O += P V on mma.sync m16n8k16 with fp32 accumulators, scores, running
 //                              maximum and sum in fp32 registers, K / V tiles double-buffered in shared memory by cp.async through the
 //                              page map.  For vdim == dim in {16, 32, 48, 64, 96, 128, 256}.
+//   softmax_attention_decode_kernel    bf16, steps of single tokens: one CTA per (row, key head, key split) with the products
+//                              TRANSPOSED (S^T = K Q^T, O^T = V^T P^T): the 16-row side of the MMA carries keys / value columns, the
+//                              8-column side the up to eight query heads of the key head, so no tensor-core row is spent on
+//                              padding; each of the four warps takes 16 keys of every 64-key tile and the warps' partial results
+//                              are merged through shared memory.
+//   softmax_attention_merge_kernel     adds the key splits' partial results.
 #pragma once
 
 #include "common.cuh"
@@ -421,6 +427,191 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
   for (int nb = 0; nb < NB; ++nb) {
     if (g < nr) *reinterpret_cast<uint32_t*>(out0 + nb * 8) = smax_pack_bf16(o[nb][0] * f0, o[nb][1] * f0);
     if (g + 8 < nr) *reinterpret_cast<uint32_t*>(out1 + nb * 8) = smax_pack_bf16(o[nb][2] * f1, o[nb][3] * f1);
+  }
+}
+
+// ---- bf16, single-token rows: transposed products ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smax_movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
+constexpr int kSdecWarps = 4, kSdecKeys = 64;
+
+inline size_t softmax_decode_smem_bytes(int dim) {
+  const size_t ring = size_t(2) * kSdecKeys * 2 * (dim + 8) * sizeof(bf16), merge = sizeof(float) * kSdecWarps * (8 * size_t(dim) + 16);
+  return ring > merge ? ring : merge;
+}
+
+template <int D16>
+__global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kernel(const SoftmaxAttnArgs<bf16> a) {
+  extern __shared__ __align__(16) unsigned char sdec_raw[];
+  constexpr int D = 16 * D16, PITCH = D + 8, KT = kSdecKeys, NT = kSdecWarps * 32;
+  bf16* const stage0 = reinterpret_cast<bf16*>(sdec_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  griddep_wait();
+  const int rep = a.heads / a.kv_heads;  // <= 8
+  const int row = blockIdx.x, kvh = blockIdx.y;
+  const int pos = a.pos[row], grp = a.group[row];
+  int lo = 0;
+  if (a.window > 0 && pos - a.window + 1 > 0) lo = pos - a.window + 1;
+  const int* pages = a.page_map + size_t(grp) * a.max_pages;
+  const size_t head_rows = size_t(kvh) * a.num_pages * a.tokens_per_page;
+  const int all_key_tiles = (pos - lo) / KT + 1;
+  const int per = (all_key_tiles + a.splits - 1) / a.splits;
+  const int tile_lo = int(blockIdx.z) * per;
+  int n_key_tiles = all_key_tiles - tile_lo < per ? all_key_tiles - tile_lo : per;
+  if (n_key_tiles < 0) n_key_tiles = 0;
+  const int first = lo + tile_lo * KT;
+
+  auto load_tile = [&](int it, int stage) {
+    bf16* sk = stage0 + size_t(stage) * 2 * KT * PITCH;
+    bf16* sv = sk + KT * PITCH;
+    const int j0 = first + it * KT;
+    constexpr int CH = D / 8;
+    for (int e = tid; e < KT * CH; e += NT) {
+      const int jj = e / CH, c = e % CH, j = j0 + jj;
+      const bool ok = j <= pos;
+      const size_t r = ok ? head_rows + size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page : 0;
+      cp_async_16(sk + jj * PITCH + c * 8, a.k_pages + r * D + c * 8, ok);
+      cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + r * D + c * 8, ok);
+    }
+    cp_async_commit();
+  };
+
+  // the group's queries as the B operand: lane (g, t) holds head g's channels kk * 16 + 2t, + 1 and + 8 + 2t, + 9
+  uint32_t qf[D16][2];
+  {
+    const bf16* q = a.q + size_t(row) * a.heads * D + (kvh * rep + (g < rep ? g : 0)) * D;
+#pragma unroll
+    for (int kk = 0; kk < D16; ++kk) {
+      qf[kk][0] = g < rep ? *reinterpret_cast<const uint32_t*>(q + kk * 16 + 2 * t) : 0u;
+      qf[kk][1] = g < rep ? *reinterpret_cast<const uint32_t*>(q + kk * 16 + 8 + 2 * t) : 0u;
+    }
+  }
+  float o[D16][4];  // O^T: (column mb * 16 + g / g + 8, head 2t / 2t + 1)
+#pragma unroll
+  for (int mb = 0; mb < D16; ++mb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[mb][e] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};  // heads 2t, 2t + 1
+
+  if (n_key_tiles > 0) load_tile(0, 0);
+  for (int it = 0; it < n_key_tiles; ++it) {
+    if (it + 1 < n_key_tiles) {
+      load_tile(it + 1, (it + 1) & 1);
+      cp_async_wait_pending(1);
+    } else {
+      cp_async_wait_pending(0);
+    }
+    __syncthreads();
+    const bf16* sk = stage0 + size_t(it & 1) * 2 * KT * PITCH;
+    const bf16* sv = sk + KT * PITCH;
+    const int j0 = first + it * KT + warp * 16;  // this warp's 16 keys
+    if (j0 <= pos) {
+      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const bf16* k0 = sk + (warp * 16 + g) * PITCH + 2 * t;
+#pragma unroll
+      for (int kk = 0; kk < D16; ++kk) {
+        uint32_t af[4];
+        af[0] = *reinterpret_cast<const uint32_t*>(k0 + kk * 16);
+        af[1] = *reinterpret_cast<const uint32_t*>(k0 + 8 * PITCH + kk * 16);
+        af[2] = *reinterpret_cast<const uint32_t*>(k0 + kk * 16 + 8);
+        af[3] = *reinterpret_cast<const uint32_t*>(k0 + 8 * PITCH + kk * 16 + 8);
+        mma_bf16_16816(c, af, qf[kk][0], qf[kk][1]);
+      }
+      // c[0], c[1]: key j0 + g, heads 2t, 2t + 1;  c[2], c[3]: key j0 + g + 8
+      const int ja = j0 + g, jb = j0 + g + 8;
+      const bool sa_ = ja <= pos && (a.window <= 0 || pos - ja < a.window), sb_ = jb <= pos && (a.window <= 0 || pos - jb < a.window);
+      c[0] = sa_ ? c[0] * a.scale : -INFINITY;
+      c[1] = sa_ ? c[1] * a.scale : -INFINITY;
+      c[2] = sb_ ? c[2] * a.scale : -INFINITY;
+      c[3] = sb_ ? c[3] * a.scale : -INFINITY;
+      float mx0 = fmaxf(c[0], c[2]), mx1 = fmaxf(c[1], c[3]);
+#pragma unroll
+      for (int sh = 4; sh < 32; sh <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+      }
+      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+      const float b0 = mn0 == -INFINITY ? 0.0f : mn0, b1 = mn1 == -INFINITY ? 0.0f : mn1;
+      const float fix0 = __expf(m_run[0] - b0), fix1 = __expf(m_run[1] - b1);
+      m_run[0] = mn0;
+      m_run[1] = mn1;
+      c[0] = __expf(c[0] - b0);
+      c[1] = __expf(c[1] - b1);
+      c[2] = __expf(c[2] - b0);
+      c[3] = __expf(c[3] - b1);
+      l_run[0] = l_run[0] * fix0 + c[0] + c[2];  // (this lane's keys; the eight lanes of a head are added at the end)
+      l_run[1] = l_run[1] * fix1 + c[1] + c[3];
+      const uint32_t pb0 = smax_movmatrix_trans(smax_pack_bf16(c[0], c[1])), pb1 = smax_movmatrix_trans(smax_pack_bf16(c[2], c[3]));
+      // V^T as the A operand: four 8 x 8 blocks (keys 0-7 / 8-15) x (columns 0-7 / 8-15) of the warp's 16 keys, transposed on load
+      const bf16* v0 = sv + (warp * 16 + (lane & 7) + 8 * (lane >> 4)) * PITCH + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int mb = 0; mb < D16; ++mb) {
+        uint32_t vf[4];
+        const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(v0 + mb * 16));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(vf[0]), "=r"(vf[1]), "=r"(vf[2]), "=r"(vf[3]) : "r"(addr));
+        o[mb][0] *= fix0;
+        o[mb][1] *= fix1;
+        o[mb][2] *= fix0;
+        o[mb][3] *= fix1;
+        mma_bf16_16816(o[mb], vf, pb0, pb1);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int sh = 4; sh < 32; sh <<= 1) {
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], sh);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], sh);
+  }
+  // merge of the four warps (the ring is free: the loop ended with a barrier)
+  float* mo = reinterpret_cast<float*>(sdec_raw);       // [warp][8 heads][D]
+  float* mm = mo + kSdecWarps * 8 * D;                  // [warp][8] maxima, then [warp][8] sums
+  float* ml = mm + kSdecWarps * 8;
+#pragma unroll
+  for (int mb = 0; mb < D16; ++mb) {
+    mo[(warp * 8 + 2 * t) * D + mb * 16 + g] = o[mb][0];
+    mo[(warp * 8 + 2 * t + 1) * D + mb * 16 + g] = o[mb][1];
+    mo[(warp * 8 + 2 * t) * D + mb * 16 + g + 8] = o[mb][2];
+    mo[(warp * 8 + 2 * t + 1) * D + mb * 16 + g + 8] = o[mb][3];
+  }
+  if (g == 0) {
+    mm[warp * 8 + 2 * t] = m_run[0];
+    mm[warp * 8 + 2 * t + 1] = m_run[1];
+    ml[warp * 8 + 2 * t] = l_run[0];
+    ml[warp * 8 + 2 * t + 1] = l_run[1];
+  }
+  __syncthreads();
+  for (int e = tid; e < rep * D; e += NT) {
+    const int hh = e / D, col = e % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kSdecWarps; ++w) M = fmaxf(M, mm[w * 8 + hh]);
+    float L = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kSdecWarps; ++w) {
+      const float mw = mm[w * 8 + hh];
+      if (mw != -INFINITY) {
+        const float f = __expf(mw - M);
+        L = fmaf(f, ml[w * 8 + hh], L);
+        acc = fmaf(f, mo[(w * 8 + hh) * D + col], acc);
+      }
+    }
+    const int h = kvh * rep + hh;
+    if (a.splits > 1) {
+      const size_t base = (size_t(blockIdx.z) * a.rows + row) * a.heads + h;
+      a.part_o[base * D + col] = acc;
+      if (col == 0) {
+        a.part_ml[base * 2] = M;
+        a.part_ml[base * 2 + 1] = L;
+      }
+    } else {
+      a.out[size_t(row) * a.ld_out + h * D + col] = __float2bfloat16_rn(acc * a.out_scale / L);
+    }
   }
 }
 
