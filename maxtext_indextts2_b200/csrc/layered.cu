@@ -708,6 +708,7 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
     ra.vdim = r.vdim;
     ra.q_scale = r.q_scale;
     ra.denom_eps = r.denom_eps;
+    ra.vec4 = (n_in % 4 == 0 && cc.rq % 4 == 0 && cc.rk % 4 == 0 && cc.rv % 4 == 0 && r.dim % 4 == 0 && r.vdim % 4 == 0) ? 1 : 0;
     if (r.kind == MTX_REC_GLA) MTX_TRY(launch_rec_scan<REC_GLA>(e, ra, b.n_runs, st));
     else MTX_TRY(launch_rec_scan<REC_MLSTM>(e, ra, b.n_runs, st));
     RecOutArgs<T> oa;

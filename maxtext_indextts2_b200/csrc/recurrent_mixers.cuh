@@ -76,6 +76,7 @@ struct RecScanArgs {
   const int* group;
   const int* pos;
   int heads, dim, vdim, chunk;
+  int vec4;            // 1: every staged row starts on a 16-byte boundary and holds whole float4s (set by the host from the sizes)
   float q_scale, denom_eps;
 };
 
@@ -99,6 +100,11 @@ inline int rec_chunk_tokens(int dim, int cb) {
   return t > 32 ? 32 : (t < kRecUnroll ? kRecUnroll : t);
 }
 inline size_t rec_scan_smem_bytes(int dim, int cb, int chunk) { return sizeof(float) * 2 * size_t(chunk) * rec_token_floats(rec_rpt(dim), cb); }
+
+__device__ __forceinline__ void rec_cp_async_16(float* dst, const float* src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 
 __device__ __forceinline__ void rec_cp_async_4(float* dst, const float* src) {
   const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
@@ -158,6 +164,29 @@ __global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const R
     const int t0 = c * TC;
     const int slots_d = kRecSlices * RPT;  // padded key channels
     const int left = (nr - t0 + kRecUnroll - 1) / kRecUnroll * kRecUnroll, TL = left < TC ? left : TC;  // tokens the walk will touch
+    if (a.vec4) {  // four channels per copy
+      constexpr int Q4 = kRecSlices * RPT / 4, C4 = CB / 4;
+      for (int e = tid; e < TL * Q4; e += NT) {
+        const int t = e / Q4, r = (e % Q4) * 4;
+        float* dst = base + t * TF + r;
+        const float* row = a.proj + size_t(r0 + t0 + t) * a.ld;
+        if (t0 + t < nr && r < d) {
+          rec_cp_async_16(dst, row + a.q_col + h * d + r);
+          rec_cp_async_16(dst + QP, row + a.k_col + h * d + r);
+          if (KIND == REC_GLA) rec_cp_async_16(dst + 2 * QP, a.aux + size_t(r0 + t0 + t) * H * d + h * d + r);
+        } else {
+          *reinterpret_cast<float4*>(dst) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          *reinterpret_cast<float4*>(dst + QP) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (KIND == REC_GLA) *reinterpret_cast<float4*>(dst + 2 * QP) = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        }
+      }
+      for (int e = tid; e < TL * C4; e += NT) {
+        const int t = e / C4, c2 = (e % C4) * 4;
+        float* dst = base + t * TF + 3 * QP + c2;
+        if (t0 + t < nr && col0 + c2 < dv) rec_cp_async_16(dst, a.proj + size_t(r0 + t0 + t) * a.ld + a.v_col + h * dv + col0 + c2);
+        else *reinterpret_cast<float4*>(dst) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    } else {
     for (int e = tid; e < TL * slots_d; e += NT) {
       const int t = e / slots_d, r = e % slots_d;
       float* dst = base + t * TF + r;
@@ -178,6 +207,7 @@ __global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const R
       float* dst = base + t * TF + 3 * QP + c2;
       if (t0 + t < nr && col0 + c2 < dv) rec_cp_async_4(dst, a.proj + size_t(r0 + t0 + t) * a.ld + a.v_col + h * dv + col0 + c2);
       else dst[0] = 0.0f;
+    }
     }
     if (KIND == REC_MLSTM) {
       for (int e = tid; e < TL * 2; e += NT) {
