@@ -63,26 +63,44 @@ struct SandwichArgs {
   int width;
 };
 
-// one CTA per row; the row of x stays in registers between the two reductions (width <= 256 * kSandwichMax)
-constexpr int kSandwichMax = 32;
+// one CTA per row; the row of x stays in registers between the two reductions.  V = 4: the row moves as float4s (width a
+// multiple of 4, <= 256 * 4 * kSandwichVec); V = 1: any width <= 256 * kSandwichMax.
+constexpr int kSandwichMax = 32, kSandwichVec = 8;
 
-template <typename T>
+template <typename T, int V>
 __global__ void __launch_bounds__(256) sandwich_step_kernel(const SandwichArgs a, T* xa) {
   __shared__ float red[8];
+  constexpr int N = V == 4 ? kSandwichVec : kSandwichMax;  // register groups of V floats per thread
   griddep_wait();
   const int r = blockIdx.x, W = a.width;
   float* xr = a.x + size_t(r) * W;
-  float xv[kSandwichMax];
+  const float* yr = a.y ? a.y + size_t(r) * W : nullptr;
+  const float* x0r = a.x0 ? a.x0 + size_t(r) * W : nullptr;
+  auto load = [&](const float* p, int c, float (&v)[V]) {
+    if (V == 4) {
+      const float4 q = *reinterpret_cast<const float4*>(p + c);
+      v[0] = q.x, v[V > 1 ? 1 : 0] = q.y, v[V > 2 ? 2 : 0] = q.z, v[V > 3 ? 3 : 0] = q.w;
+    } else {
+      v[0] = p[c];
+    }
+  };
+  float yv[N][V];
   float f = 0.0f;
-  if (a.y) {
-    const float* yr = a.y + size_t(r) * W;
+  if (yr) {
     float ss = 0.0f;
 #pragma unroll
-    for (int u = 0; u < kSandwichMax; ++u) {
-      const int c = threadIdx.x + u * 256;
+    for (int u = 0; u < N; ++u) {
+      const int c = (threadIdx.x + u * 256) * V;
       if (c < W) {
-        const float v = yr[c] + (a.y_bias ? a.y_bias[c] : 0.0f);
-        ss = fmaf(v, v, ss);
+        float b[V];
+        load(yr, c, yv[u]);
+        if (a.y_bias) {
+          load(a.y_bias, c, b);
+#pragma unroll
+          for (int e = 0; e < V; ++e) yv[u][e] += b[e];
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) ss = fmaf(yv[u][e], yv[u][e], ss);
       }
     }
     ss = block_sum(ss, red);
@@ -90,25 +108,49 @@ __global__ void __launch_bounds__(256) sandwich_step_kernel(const SandwichArgs a
   }
   float ss2 = 0.0f;
 #pragma unroll
-  for (int u = 0; u < kSandwichMax; ++u) {
-    const int c = threadIdx.x + u * 256;
+  for (int u = 0; u < N; ++u) {
+    const int c = (threadIdx.x + u * 256) * V;
     if (c < W) {
-      float v = xr[c];
-      if (a.y) v += (a.y[size_t(r) * W + c] + (a.y_bias ? a.y_bias[c] : 0.0f)) * f * (1.0f + a.post[c]);
-      if (a.x0) v += a.x0[size_t(r) * W + c];
-      if (a.add_vec) v += a.add_vec[c];
-      xv[u] = v;
-      ss2 = fmaf(v, v, ss2);
-      if (a.y || a.x0 || a.add_vec) xr[c] = v;
+      float v[V], w[V];
+      load(xr, c, v);
+      if (yr) {
+        load(a.post, c, w);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] += yv[u][e] * f * (1.0f + w[e]);
+      }
+      if (x0r) {
+        load(x0r, c, w);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] += w[e];
+      }
+      if (a.add_vec) {
+        load(a.add_vec, c, w);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] += w[e];
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        yv[u][e] = v[e];  // (the registers now hold the new x)
+        ss2 = fmaf(v[e], v[e], ss2);
+      }
+      if (yr || x0r || a.add_vec) {
+        if (V == 4) *reinterpret_cast<float4*>(xr + c) = make_float4(v[0], v[V > 1 ? 1 : 0], v[V > 2 ? 2 : 0], v[V > 3 ? 3 : 0]);
+        else xr[c] = v[0];
+      }
     }
   }
   if (!a.pre) return;
   ss2 = block_sum(ss2, red);
   const float f2 = 1.0f / sqrtf(ss2 / float(W) + a.eps);
 #pragma unroll
-  for (int u = 0; u < kSandwichMax; ++u) {
-    const int c = threadIdx.x + u * 256;
-    if (c < W) xa[size_t(r) * W + c] = to_act<T>(xv[u] * f2 * (1.0f + a.pre[c]));
+  for (int u = 0; u < N; ++u) {
+    const int c = (threadIdx.x + u * 256) * V;
+    if (c < W) {
+      float w[V];
+      load(a.pre, c, w);
+#pragma unroll
+      for (int e = 0; e < V; ++e) xa[size_t(r) * W + c + e] = to_act<T>(yv[u][e] * f2 * (1.0f + w[e]));
+    }
   }
 }
 

@@ -464,23 +464,40 @@ CompositeCols composite_cols(const mtx_layer_desc& l) {
   return cc;
 }
 
-template <int KIND, int CB>
-int launch_rec_scan_cb(const RecScanArgs& ra, int n_runs, cudaStream_t st) {
-  const dim3 grid(n_runs, ra.heads, (ra.vdim + CB - 1) / CB), block(CB * kRecSlices);
-  const size_t smem = rec_scan_smem_bytes(ra.dim, CB, ra.chunk);
-  const int rpt = rec_rpt(ra.dim);
-  if (rpt == 4) return launch(recurrent_scan_kernel<KIND, 4, CB>, grid, block, smem, st, ra);
-  if (rpt == 8) return launch(recurrent_scan_kernel<KIND, 8, CB>, grid, block, smem, st, ra);
-  if (rpt == 16) return launch(recurrent_scan_kernel<KIND, 16, CB>, grid, block, smem, st, ra);
-  return launch(recurrent_scan_kernel<KIND, 32, CB>, grid, block, smem, st, ra);
+template <int KIND, int RPT, int CB, int SL>
+int launch_rec_scan_t(const RecScanArgs& ra, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  static size_t have = 0;  // per instantiation
+  if (smem > 48 * 1024 && smem > have) {
+    MTX_CUDA(cudaFuncSetAttribute(recurrent_scan_kernel<KIND, RPT, CB, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    have = smem;
+  }
+  return launch(recurrent_scan_kernel<KIND, RPT, CB, SL>, grid, block, smem, st, ra);
 }
 
-// 16 value columns per CTA when that still gives every SM two CTAs, else 8 (a walk is bound by latency: more CTAs, more overlap)
+template <int KIND, int CB, int SL>
+int launch_rec_scan_cb(const RecScanArgs& ra, int n_runs, cudaStream_t st) {
+  const dim3 grid(n_runs, ra.heads, (ra.vdim + CB - 1) / CB), block(CB * SL);
+  const size_t smem = rec_scan_smem_bytes(ra.dim, CB, SL, ra.chunk);
+  const int rpt = rec_rpt(ra.dim, SL);
+  if (rpt == 4) return launch_rec_scan_t<KIND, 4, CB, SL>(ra, grid, block, smem, st);
+  if (rpt == 8) return launch_rec_scan_t<KIND, 8, CB, SL>(ra, grid, block, smem, st);
+  if (rpt == 16) return launch_rec_scan_t<KIND, 16, CB, SL>(ra, grid, block, smem, st);
+  if constexpr (SL == 8) return launch_rec_scan_t<KIND, 32, CB, SL>(ra, grid, block, smem, st);
+  return fail(MTX_ERR_UNSUPPORTED, "recurrence: dim %d", ra.dim);
+}
+
+// A walk is bound by latency, so what counts is how many warps share an SM.  16 value columns per CTA when that still gives every
+// SM two CTAs, else 8; and when even 8-column CTAs with 8 slices per column leave the thread slots of the GPU mostly empty (one
+// prompt: heads x vdim columns in all), a column is cut into 16 slices.
 template <int KIND>
-int launch_rec_scan(mtx_layered* e, RecScanArgs& ra, int n_runs, cudaStream_t st) {
+int launch_rec_scan(mtx_layered* e, RecScanArgs& ra, int n_runs, int rows, cudaStream_t st) {
+  const long long columns = (long long)n_runs * ra.heads * ra.vdim;
   const bool wide = (long long)n_runs * ra.heads * ((ra.vdim + 15) / 16) >= 2LL * e->num_sms;
-  ra.chunk = rec_chunk_tokens(ra.dim, wide ? 16 : 8);
-  return wide ? launch_rec_scan_cb<KIND, 16>(ra, n_runs, st) : launch_rec_scan_cb<KIND, 8>(ra, n_runs, st);
+  static const int force_sl = env_int("MTX_REC_SLICES", 0);
+  const bool fine = force_sl ? force_sl == 16 : (!wide && ra.dim >= 64 && columns * 8 < 512LL * e->num_sms);
+  ra.chunk = rec_chunk_tokens(ra.dim, wide ? 16 : 8, fine ? 16 : 8, rows == n_runs);
+  if (fine && ra.dim >= 16) return launch_rec_scan_cb<KIND, 8, 16>(ra, n_runs, st);
+  return wide ? launch_rec_scan_cb<KIND, 16, 8>(ra, n_runs, st) : launch_rec_scan_cb<KIND, 8, 8>(ra, n_runs, st);
 }
 
 // MTX_NORM_SANDWICH: x += wnorm(y + bias, post), then what comes before the next sublayer: the pre-adds of the next layer run
@@ -504,7 +521,8 @@ int sandwich_step(mtx_layered* e, const float* y, const float* bias, const float
     sa.pre = nl.norm1;
   }
   if (!sa.y && !sa.x0 && !sa.add_vec && !sa.pre) return MTX_OK;
-  return launch(sandwich_step_kernel<T>, dim3(rows), dim3(256), 0, st, sa, static_cast<T*>(e->xa));
+  if (sa.width % 4 == 0 && sa.width <= 256 * 4 * kSandwichVec) return launch(sandwich_step_kernel<T, 4>, dim3(rows), dim3(256), 0, st, sa, static_cast<T*>(e->xa));
+  return launch(sandwich_step_kernel<T, 1>, dim3(rows), dim3(256), 0, st, sa, static_cast<T*>(e->xa));
 }
 
 bool use_softmax_mma() {
@@ -709,8 +727,8 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
     ra.q_scale = r.q_scale;
     ra.denom_eps = r.denom_eps;
     ra.vec4 = (n_in % 4 == 0 && cc.rq % 4 == 0 && cc.rk % 4 == 0 && cc.rv % 4 == 0 && r.dim % 4 == 0 && r.vdim % 4 == 0) ? 1 : 0;
-    if (r.kind == MTX_REC_GLA) MTX_TRY(launch_rec_scan<REC_GLA>(e, ra, b.n_runs, st));
-    else MTX_TRY(launch_rec_scan<REC_MLSTM>(e, ra, b.n_runs, st));
+    if (r.kind == MTX_REC_GLA) MTX_TRY(launch_rec_scan<REC_GLA>(e, ra, b.n_runs, rows, st));
+    else MTX_TRY(launch_rec_scan<REC_MLSTM>(e, ra, b.n_runs, rows, st));
     RecOutArgs<T> oa;
     memset(&oa, 0, sizeof(oa));
     oa.o = e->rec_o;

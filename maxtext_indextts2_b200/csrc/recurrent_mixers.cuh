@@ -81,25 +81,30 @@ struct RecScanArgs {
 };
 
 // A CTA owns CB value columns of one (run, head): thread (column jl, slice sl) keeps RPT key channels of its column of S in
-// registers, in groups of four: channels g * 32 + sl * 4 .. + 3 for g < RPT / 4 (8 slices: dim <= 8 * RPT), so that the eight
-// slices of a column read 128 contiguous bytes of the state and of the staged q / k / decays at a time.  The run's q / k / decays (or gates)
-// / v arrive in chunks of `chunk` tokens (a multiple of 4) through a two-stage cp.async ring; tokens are walked four at a time
+// registers, in groups of four: channels g * 4 SL + sl * 4 .. + 3 for g < RPT / 4 (SL = 8 or 16 slices: dim <= SL * RPT), so that the
+// slices of a column read 128 (256) contiguous bytes of the state and of the staged q / k / decays at a time.  The run's q / k / decays (or gates)
+// / v arrive in chunks of `chunk` tokens (a multiple of 4) through a four-stage cp.async ring; tokens are walked four at a time
 // so that the four read-outs' reductions overlap (the state update itself is the only chain from token to token).
-constexpr int kRecSlices = 8, kRecUnroll = 4;
+constexpr int kRecSlices = 8, kRecUnroll = 4;  // (kRecSlices: the default; short of CTAs, a column is cut into 16 slices: SL)
 
 // floats of one token in a stage: q, k, decays (8 * RPT channels each), then CB values, then 4 scalars (mLSTM: log input gate,
 // log forget gate; later keep, put, floor)
-__host__ __device__ inline int rec_token_floats(int rpt, int cb) { return 3 * kRecSlices * rpt + cb + 4; }
-inline int rec_rpt(int dim) {
-  const int r = (dim + kRecSlices - 1) / kRecSlices;
+__host__ __device__ inline int rec_token_floats(int rpt, int cb, int sl) { return 3 * sl * rpt + cb + 4; }
+inline int rec_rpt(int dim, int sl) {
+  const int r = (dim + sl - 1) / sl;
   return r <= 4 ? 4 : (r <= 8 ? 8 : (r <= 16 ? 16 : 32));
 }
-inline int rec_chunk_tokens(int dim, int cb) {
-  int t = (48 * 1024) / int(sizeof(float) * 2 * rec_token_floats(rec_rpt(dim), cb));
+constexpr int kRecStages = 4;  // chunks in the cp.async ring: three are in flight while one is walked
+// tokens per chunk: 16 for prompt portions (as many as 96 KB of ring hold, at least 4), 4 when every run is a single token
+inline int rec_chunk_tokens(int dim, int cb, int sl, bool single_tokens) {
+  if (single_tokens) return kRecUnroll;
+  int t = (96 * 1024) / int(sizeof(float) * kRecStages * rec_token_floats(rec_rpt(dim, sl), cb, sl));
   t = t / kRecUnroll * kRecUnroll;
-  return t > 32 ? 32 : (t < kRecUnroll ? kRecUnroll : t);
+  return t > 16 ? 16 : (t < kRecUnroll ? kRecUnroll : t);
 }
-inline size_t rec_scan_smem_bytes(int dim, int cb, int chunk) { return sizeof(float) * 2 * size_t(chunk) * rec_token_floats(rec_rpt(dim), cb); }
+inline size_t rec_scan_smem_bytes(int dim, int cb, int sl, int chunk) {
+  return sizeof(float) * kRecStages * size_t(chunk) * rec_token_floats(rec_rpt(dim, sl), cb, sl);
+}
 
 __device__ __forceinline__ void rec_cp_async_16(float* dst, const float* src) {
   const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
@@ -111,12 +116,12 @@ __device__ __forceinline__ void rec_cp_async_4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-template <int KIND, int RPT, int CB>
-__global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const RecScanArgs a) {
+template <int KIND, int RPT, int CB, int SL>
+__global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanArgs a) {
   extern __shared__ __align__(16) float rec_smem[];
-  constexpr int NT = CB * kRecSlices, QP = kRecSlices * RPT, TF = 3 * QP + CB + 4, GS = 4 * kRecSlices;  // GS: channels per group of float4s
+  constexpr int NT = CB * SL, QP = SL * RPT, TF = 3 * QP + CB + 4, GS = 4 * SL;  // GS: channels per group of float4s
   const int d = a.dim, dv = a.vdim, H = a.heads, TC = a.chunk;
-  const int tid = threadIdx.x, jl = tid / kRecSlices, sl = tid % kRecSlices;
+  const int tid = threadIdx.x, jl = tid / SL, sl = tid % SL;
   griddep_wait();
   const int r0 = a.run_row0[blockIdx.x], nr = a.run_row0[blockIdx.x + 1] - r0, h = blockIdx.y;
   if (nr <= 0) return;
@@ -160,12 +165,16 @@ __global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const R
   // stage <- chunk c: every element by a 4-byte cp.async (the projection's columns have no alignment to count on); the tail of
   // the last chunk and the key channels beyond dim are filled with values that leave the state alone (k = v = q = 0, decay 1)
   auto load_chunk = [&](int c, int stage) {
+    if (c >= n_chunks) {  // (an empty group keeps the count of groups per iteration uniform)
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return;
+    }
     float* base = rec_smem + size_t(stage) * TC * TF;
     const int t0 = c * TC;
-    const int slots_d = kRecSlices * RPT;  // padded key channels
+    const int slots_d = SL * RPT;  // padded key channels
     const int left = (nr - t0 + kRecUnroll - 1) / kRecUnroll * kRecUnroll, TL = left < TC ? left : TC;  // tokens the walk will touch
     if (a.vec4) {  // four channels per copy
-      constexpr int Q4 = kRecSlices * RPT / 4, C4 = CB / 4;
+      constexpr int Q4 = SL * RPT / 4, C4 = CB / 4;
       for (int e = tid; e < TL * Q4; e += NT) {
         const int t = e / Q4, r = (e % Q4) * 4;
         float* dst = base + t * TF + r;
@@ -220,16 +229,12 @@ __global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const R
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  load_chunk(0, 0);
+  for (int c = 0; c < kRecStages - 1; ++c) load_chunk(c, c);
   for (int c = 0; c < n_chunks; ++c) {
-    if (c + 1 < n_chunks) {
-      load_chunk(c + 1, (c + 1) & 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+    load_chunk(c + kRecStages - 1, (c + kRecStages - 1) % kRecStages);  // (its stage was walked in iteration c - 1)
+    asm volatile("cp.async.wait_group %0;" ::"n"(kRecStages - 1) : "memory");
     __syncthreads();
-    float* base = rec_smem + size_t(c & 1) * TC * TF;
+    float* base = rec_smem + size_t(c % kRecStages) * TC * TF;
     const int t0 = c * TC;
     const int left = (nr - t0 + kRecUnroll - 1) / kRecUnroll * kRecUnroll, TL = left < TC ? left : TC;
     if (KIND == REC_MLSTM) {
@@ -267,8 +272,8 @@ __global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const R
           const float* al = k + QP;
 #pragma unroll
           for (int i4 = 0; i4 < RPT; i4 += 4) {
-            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * kRecSlices), q4 = *reinterpret_cast<const float4*>(q + i4 * kRecSlices),
-                         a4 = *reinterpret_cast<const float4*>(al + i4 * kRecSlices);
+            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * SL), q4 = *reinterpret_cast<const float4*>(q + i4 * SL),
+                         a4 = *reinterpret_cast<const float4*>(al + i4 * SL);
             S[i4] = fmaf(a4.x, S[i4], k4.x * v);
             S[i4 + 1] = fmaf(a4.y, S[i4 + 1], k4.y * v);
             S[i4 + 2] = fmaf(a4.z, S[i4 + 2], k4.z * v);
@@ -283,7 +288,7 @@ __global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const R
           floor_m[u] = tok[3 * QP + CB + 2];
 #pragma unroll
           for (int i4 = 0; i4 < RPT; i4 += 4) {
-            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * kRecSlices), q4 = *reinterpret_cast<const float4*>(q + i4 * kRecSlices);
+            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * SL), q4 = *reinterpret_cast<const float4*>(q + i4 * SL);
             const float pk[4] = {put * k4.x, put * k4.y, put * k4.z, put * k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -296,7 +301,7 @@ __global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const R
         }
       }
 #pragma unroll
-      for (int o = 1; o < kRecSlices; o <<= 1) {
+      for (int o = 1; o < SL; o <<= 1) {
 #pragma unroll
         for (int u = 0; u < kRecUnroll; ++u) {
           part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
@@ -317,7 +322,7 @@ __global__ void __launch_bounds__(CB * kRecSlices) recurrent_scan_kernel(const R
         a.o[size_t(r0 + t0 + t + sl) * H * dv + h * dv + j] = out;
       }
     }
-    __syncthreads();  // the stage is free for the chunk after next
+    __syncthreads();  // the stage is free for the next iteration's load
   }
   const bool write_n = KIND == REC_MLSTM && blockIdx.z == 0 && jl == 0;
 #pragma unroll
