@@ -410,3 +410,52 @@ def test_greedy_generation_through_the_offline_engine():
       assert float(top2[1] - top2[0]) > 1e-4, "near-tie in the test's own model; change the seed"
       seq.append(int(logits.argmax()))
     assert out.token_ids.tolist() == seq[len(prompt):]
+
+
+# ---- the command line: a trace of batched steps replayed through bin/trace_run --------------------------------------------------------
+
+@pytest.mark.parametrize("dtype,tol", [("float32", TIGHT), ("bfloat16", 5e-2)])  # (bfloat16: per step, some of few rows)
+def test_trace_runner_replays_a_mixed_schedule(tmp_path, dtype, tol):
+  import json
+  import os
+  import subprocess
+
+  from tests.test_gugidra_host import _write_safetensors
+
+  cfg = DEFAULT()
+  t = ref.random_model(cfg, seed=23)
+  model_dir = tmp_path / "model"
+  os.makedirs(model_dir)
+  with open(model_dir / "config.json", "w") as f:
+    json.dump(cfg, f)
+  _write_safetensors(model_dir / "model.safetensors", as_torch(t))
+  lens = {"a": 70, "b": 9, "c": 33, "d": 5, "e": 40, "f": 20}
+  toks = {k: tokens_for(cfg, n, seed=ord(k)) for k, n in lens.items()}
+  # four pages of 64 tokens: a, b, c fill them (2 + 1 + 1); d, e and f fit only into what b and c give back, and take their slots
+  plan = [[("a", 30), ("b", 2)], [("a", 1), ("b", 7), ("c", 33)], [("a", 35), ("d", 2)], [("a", 1), ("d", 3), ("e", 39)], [("a", 3), ("e", 1), ("f", 20)]]
+  at = {k: 0 for k in toks}
+  lines, rows = [], []
+  for n, step in enumerate(plan):
+    entries, end = [], []
+    for k, c in step:
+      entries.append({"id": k, "tokens": toks[k][at[k] : at[k] + c], "want": list(range(c))})
+      rows.append((n, k, at[k], c))
+      at[k] += c
+      if at[k] == lens[k]:
+        end.append(k)
+    lines.append(json.dumps({"step": n, "entries": entries, "end": end}))
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  out_dir = tmp_path / "out"
+  p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out", str(out_dir), "--max-tokens", "256"],
+                     input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+  assert p.returncode == 0, p.stderr[-2000:]
+  assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {n}" for n in range(len(plan))]
+  want = {k: ref.logits_of(cfg, t, v) for k, v in toks.items()}
+  V = cfg["vocab"]
+  errs = []
+  for n in range(len(plan)):
+    got = np.fromfile(out_dir / f"{n}.f32", dtype="<f4").reshape(-1, V)
+    exp = np.concatenate([want[k][lo : lo + c] for s, k, lo, c in rows if s == n])
+    assert got.shape == exp.shape
+    errs.append(rms_err(got, exp))
+  assert max(errs) < tol, errs
