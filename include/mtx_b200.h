@@ -383,7 +383,7 @@ typedef struct {
   int32_t values_are_keys; /* 1: the value of a token is its key as projected (before the rotation); needs vdim == dim */
   float scale;             /* multiplies <q, k> */
   float out_scale;
-  const float* rot_freq;   /* [rot_dims / 2] radians per position of pair i */
+  const double* rot_freq;  /* [rot_dims / 2] radians per position of pair i */
   void* k_pages;           /* [kv_heads, num_pages, tokens_per_page, dim] */
   void* v_pages;           /* [kv_heads, num_pages, tokens_per_page, vdim] */
 } mtx_softmax_attn_desc;

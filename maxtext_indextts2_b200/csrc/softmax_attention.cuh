@@ -6,8 +6,9 @@
 //   p(j)  = exp(s(j) - max_j s) / sum_j exp(s(j) - max_j s)
 //   out_h = out_scale * sum_j p(j) v_g(j)
 //
-// rot(t, p) turns the channel pairs (2c, 2c + 1), c < rot_dims / 2, of a head by the angle p * rot_freq[c] (fp32 angle, fp32
-// sine and cosine); the remaining channels pass.  A design whose values are the un-rotated keys (values_are_keys) gets the key
+// rot(t, p) turns the channel pairs (2c, 2c + 1), c < rot_dims / 2, of a head by the angle p * rot_freq[c]; the product and its
+// reduction to [-pi, pi] are formed in double (so that the angle of a late position is no worse than that of an early one),
+// sine and cosine in fp32; the remaining channels pass.  A design whose values are the un-rotated keys (values_are_keys) gets the key
 // projection written twice: rotated into the key pool, as projected into the value pool.
 //
 //   rope_append_kernel         per row: bias already in the projection; rotates q and k, writes q, appends k and v to the pages
@@ -39,7 +40,7 @@ struct RopeAppendArgs {
   const float* proj;     // [rows, ld]: q at column q_col, k at k_col, v at v_col (v_col < 0: the values are the keys)
   long long ld;
   int q_col, k_col, v_col;
-  const float* rot_freq;  // [rot_dims / 2]
+  const double* rot_freq;  // [rot_dims / 2]
   T* q_out;               // [rows, H * d]
   T* k_pages;
   T* v_pages;
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendArgs<T
   const float* row = a.proj + size_t(r) * a.ld;
   const int p = a.pos[r], grp = a.group[r];
   const size_t slot = size_t(a.page_map[size_t(grp) * a.max_pages + p / a.tokens_per_page]) * a.tokens_per_page + p % a.tokens_per_page;
-  const float fp = float(p);
+  const double dp = double(p);
   // pairs of q and of k: unit u = (head, pair)
   const int q_pairs = H * half, k_pairs = G * half;
   for (int u = tid; u < q_pairs + k_pairs; u += blockDim.x) {
@@ -68,7 +69,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendArgs<T
     float x0 = src[0], x1 = src[1];
     if (c < rh) {
       float sn, cs;
-      sincosf(fp * a.rot_freq[c], &sn, &cs);
+      const double ang = dp * a.rot_freq[c];
+      sincosf(float(ang - 6.283185307179586 * rint(ang * 0.15915494309189535)), &sn, &cs);
       const float y0 = x0 * cs - x1 * sn, y1 = x1 * cs + x0 * sn;
       x0 = y0;
       x1 = y1;

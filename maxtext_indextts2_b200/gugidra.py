@@ -134,9 +134,10 @@ def _shape(t: torch.Tensor, shape, name: str) -> torch.Tensor:
 
 
 def rot_frequencies(dims: int, base: float) -> torch.Tensor:
-  """Radians per position of the channel pair i < dims / 2: base^(-2i / dims), evaluated in float64 and rounded once."""
+  """Radians per position of the channel pair i < dims / 2: base^(-2i / dims), in float64 (the device multiplies it by the
+  position in double and reduces the angle before the fp32 sine and cosine)."""
   i = np.arange(dims // 2, dtype=np.float64)
-  return torch.from_numpy((float(base) ** (-2.0 * i / dims)).astype(np.float32))
+  return torch.from_numpy(float(base) ** (-2.0 * i / dims))
 
 
 def layer_plan(config, tensors: Dict[str, torch.Tensor], i: int) -> Dict[str, Any]:

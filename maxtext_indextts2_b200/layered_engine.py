@@ -97,7 +97,9 @@ class LayeredParams:
     for lp in plan["layers"]:
       d = pack(lp, _LAYER_MATS, _LAYER_VECS)
       if d.get("attn"):
-        d["attn"] = pack(d["attn"], (), _ATTN_VECS)
+        d["attn"] = dict(d["attn"])
+        for k in _ATTN_VECS:  # (the rotation's frequencies stay float64)
+          d["attn"][k] = put(d["attn"].get(k), torch.float64)
       if d.get("rec"):
         d["rec"] = pack(d["rec"], (), _REC_VECS)
       if d.get("moe"):

@@ -324,6 +324,8 @@ SIZES = {
     "key_size_over_the_smallest_register_tile": lambda: model([par(r_dim=40), gla(dim=72, vdim=8)]),
     "wide_recurrent_heads": lambda: model([gla(heads=2, dim=136, vdim=40)], width=64),
     "big_attention_heads": lambda: model([par(heads=2, kv_heads=1, dim=72, rot_dims=40)], width=64),
+    "attention_heads_beyond_the_default_shared_memory": lambda: model([par(heads=2, kv_heads=1, dim=160, rot_dims=64)], width=64),
+    "widest_recurrent_heads": lambda: model([gla(heads=1, dim=256, vdim=16), par(heads=2, kv_heads=2, dim=16, r_heads=1, r_dim=200, r_vdim=24)], width=64),
     "groups_all_kept": lambda: model([gla(MOE(groups=3, keep=3))]),
     "one_expert_per_group": lambda: model([gla(MOE(experts=6, groups=6, keep=3, top=3))]),
     "every_expert_of_the_kept_groups": lambda: model([gla(MOE(experts=8, groups=4, keep=2, top=4))]),
